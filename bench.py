@@ -1,0 +1,388 @@
+"""Benchmark of the quantized-KV decode hot path.
+
+Workload (the 32K-token single-layer decode-attention configuration): one layer,
+32 query / 8 KV heads, head_dim 128, 32768 cached tokens per sequence (255 packed
+key pages, 254 packed value pages, fp16 tails), bf16 Gaussian K with 4 outlier
+channels per head (x8), batch rows sharded over the GPUs (weak scaling: every
+GPU holds `--batch` sequences).  One step = one decode step of that layer
+through the cache object: append the new token's K/V, fused dequant decode
+attention, flush a full Q-buffer if there is one.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference]
+
+Prints one JSON line (rank 0).  `value` is device-timed with the step inputs
+already in HBM; `e2e` runs the same step through the public API from pinned
+host tensors with the result copied back every step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+H_KV, H_Q, D, CTX = 8, 32, 128, 32768
+K_PAGE_BYTES, V_PAGE_BYTES = 5760, 4608     # packed record + fp16 metadata per (page, kv-head)
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=128, help="sequences per GPU")
+    ap.add_argument("--ctx", type=int, default=CTX)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sweep", action="store_true", help="also time batch 1/8/32 (attention call only)")
+    return ap.parse_args()
+
+
+# --------------------------------------------------------------------------- #
+# byte accounting (per sequence = per batch row, all 8 KV heads)
+# --------------------------------------------------------------------------- #
+def packed_bytes(pages_k: int, pages_v: int) -> int:
+    return H_KV * (pages_k * K_PAGE_BYTES + pages_v * V_PAGE_BYTES)
+
+
+def attention_bytes(lay) -> int:
+    """Algorithmic bytes of one attention call per sequence: packed pages + fp16 tails + page tables + q/out."""
+    g = H_Q // H_KV
+    tails = (2 * lay.Sink_Count + lay.Q_Buffer_Count_K + lay.Q_Buffer_Count_V + lay.Local_Count_V) * 256
+    per_head = (lay.PageCount_K * K_PAGE_BYTES + lay.PageCount_V * V_PAGE_BYTES + tails
+                + (lay.PageCount_K + lay.PageCount_V) * 8 + 2 * g * 256)
+    return H_KV * per_head
+
+
+# --------------------------------------------------------------------------- #
+# clocks during the timed region (read-only NVML queries)
+# --------------------------------------------------------------------------- #
+class ClockSampler:
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._t = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+                 "hw_power_brake_slowdown": 0x80}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h) if hasattr(
+                    nv, "nvmlDeviceGetCurrentClocksEventReasons") else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for n, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._t = threading.Thread(target=self._run, daemon=True)
+            self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._t is not None:
+            self._t.join()
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# --------------------------------------------------------------------------- #
+# reference arm / CPU baseline: the reference's PyTorch path on the host cores
+# --------------------------------------------------------------------------- #
+def cpu_reference(ctx: int, steps: int, warmup: int, budget_s: float = 25.0):
+    """Times decode steps of the reference's PyTorch (fake-quant + eager attention) path, fp32, on all host
+    cores, for ONE sequence of the workload (8 KV heads, `ctx` cached tokens)."""
+    from oracle import kitty_sim_port as sp
+
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(cores)
+    g = torch.Generator().manual_seed(0)
+    k = torch.randn(1, H_KV, ctx, D, generator=g)
+    for h in range(H_KV):
+        k[:, h, :, torch.randperm(D, generator=g)[:4]] *= 8.0
+    v = torch.randn(1, H_KV, ctx, D, generator=g)
+    cache = sp.SimKittyCache()
+    cache.update(k, v)
+    del k, v
+    scaling = D ** -0.5
+    times = []
+    t_begin = time.perf_counter()
+    for s in range(warmup + steps):
+        q = torch.randn(1, H_Q, 1, D, generator=g)
+        kt, vt = torch.randn(1, H_KV, 1, D, generator=g), torch.randn(1, H_KV, 1, D, generator=g)
+        t0 = time.perf_counter()
+        sp.decode_step(cache, q, kt, vt, scaling)
+        dt = time.perf_counter() - t0
+        if s >= warmup:
+            times.append(dt)
+        if s >= warmup + 2 and time.perf_counter() - t_begin > budget_s:
+            break
+    from oracle.kitty_oracle import prefill_partition
+
+    p = prefill_partition(ctx)
+    per_step = sum(times) / len(times)
+    gbs = packed_bytes(p["pages_k"], p["pages_v"]) / per_step / 1e9
+    return {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
+            "sample": f"1 sequence (8 KV heads, {ctx} tokens), {len(times)} decode steps, fp32, torch on {cores} threads; "
+                      "bytes counted as the packed-KV bytes of that sequence",
+            "ms_per_step": per_step * 1e3, "steps": len(times), "tokens_per_s": 1.0 / per_step}
+
+
+# --------------------------------------------------------------------------- #
+def build_cache(kb, batch, ctx, extra, device, seed):
+    cfg = argparse.Namespace(num_hidden_layers=1, head_dim=D, num_key_value_heads=H_KV, num_attention_heads=H_Q,
+                             hidden_size=H_Q * D)
+    cache = kb.KittyCache(cfg, batch, ctx + extra + 256, device=device)
+    g = torch.Generator(device=device).manual_seed(seed)
+    # the prompt is generated and quantized in slices of 16 sequences to bound transient memory
+    lay = cache.kv_cache[0]
+    from kitty_b200 import _lib
+    from oracle.kitty_oracle import prefill_partition
+
+    p = prefill_partition(ctx)
+    for b0 in range(0, batch, 16):
+        b1 = min(batch, b0 + 16)
+        k = torch.randn(b1 - b0, H_KV, ctx, D, generator=g, device=device, dtype=torch.float32)
+        for h in range(H_KV):
+            k[:, h, :, torch.randperm(D, generator=g, device=device)[:4]] *= 8.0
+        k = k.to(torch.bfloat16)
+        v = torch.randn(b1 - b0, H_KV, ctx, D, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+        sub = _lib.KittyLayer.from_buffer_copy(lay.c_layer())
+        for name, rows in (("Sink_Buffer_K", 32), ("Sink_Buffer_V", 32), ("Q_Buffer_K", 128), ("Q_Buffer_V", 128),
+                           ("Local_Buffer_V", 128)):
+            setattr(sub, name, getattr(lay, name)[b0].data_ptr())
+        rc = _lib.lib().kitty_prefill_tails(sub, k.data_ptr(), v.data_ptr(), _lib.KITTY_BF16, k.stride(0), k.stride(1),
+                                            k.stride(2), v.stride(0), v.stride(1), v.stride(2), b1 - b0, ctx, p["sink"],
+                                            p["qbuf_k"], p["local_v"], p["qbuf_v"], _lib.stream_ptr(k.device))
+        _lib.check(rc, "kitty_prefill_tails")
+        kb.quantize_pack_k(k, p["sink"], p["pages_k"], lay.PageTable_K[b0:b1], 0, lay.KeyCache, lay.KeyCache_metadata, 128, 32)
+        kb.quantize_pack_v(v, p["sink"], p["pages_v"], lay.PageTable_V[b0:b1], 0, lay.ValueCache, lay.ValueCache_metadata, 128)
+        del k, v
+    lay.Sink_Count, lay.Q_Buffer_Count_K, lay.Local_Count_V, lay.Q_Buffer_Count_V = p["sink"], p["qbuf_k"], p["local_v"], p["qbuf_v"]
+    lay.PageCount_K, lay.PageCount_V = p["pages_k"], p["pages_v"]
+    torch.cuda.synchronize(device)
+    return cache
+
+
+def main():
+    args = parse()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        r = cpu_reference(args.ctx, args.steps, args.warmup, budget_s=120.0)
+        line = {"impl": "reference", "metric": "decode_attn_packed_kv_throughput", "value": r["value"], "unit": "GB/s",
+                "n_gpus": args.gpus, "steps": r["steps"], "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": f"decode step, 1 layer, 32q/8kv heads, head_dim 128, {args.ctx} cached tokens",
+                           "batch_per_gpu": 1, "l2": "inputs larger than L2"},
+                "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+                "decode_tokens_per_s": r["tokens_per_s"],
+                "e2e": {"value": r["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (kitty_b200 has no CPU path)")
+    import kitty_b200 as kb
+    from kitty_b200 import _lib
+
+    _lib.lib()
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+
+    B, W, K = args.batch, args.warmup, args.steps
+    if W < 3:
+        W = 3
+    total = 2 * (W + K)                         # device-timed pass, then the end-to-end pass
+    cache = build_cache(kb, B, args.ctx, total, device, seed=1234 + rank)
+    lay = cache.kv_cache[0]
+    mod = argparse.Namespace(num_attention_heads=H_Q, num_key_value_heads=H_KV)
+    scaling = D ** -0.5
+    g = torch.Generator(device=device).manual_seed(99 + rank)
+    qs = torch.randn(total, B, H_Q, 1, D, generator=g, device=device).to(torch.bfloat16)
+    ks = torch.randn(total, B, H_KV, 1, D, generator=g, device=device).to(torch.bfloat16)
+    vs = torch.randn(total, B, H_KV, 1, D, generator=g, device=device).to(torch.bfloat16)
+    launches = {"n": 0}
+
+    def step(q, k, v):
+        cache.update(k, v, 0)
+        out, _ = kb.kitty_attention_forward(mod, q, lay, scaling)
+        flush = lay.Q_Buffer_Count_K == 128 or lay.Q_Buffer_Count_V == 128
+        cache.quantize_decode(0)
+        launches["n"] += 4 + (1 if flush else 0)      # append, streaming, plain, merge (+ flush)
+        return out
+
+    def barrier():
+        torch.cuda.synchronize(device)
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    # ---------------- device-timed pass: inputs resident in HBM ---------------- #
+    for i in range(W):
+        step(qs[i], ks[i], vs[i])
+    barrier()
+    launches["n"] = 0
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    attn_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    packed = attn_alg = 0
+    with ClockSampler(local_rank) as clocks:
+        ev0.record()
+        for i in range(K):
+            q, k, v = qs[W + i], ks[W + i], vs[W + i]
+            cache.update(k, v, 0)
+            packed += B * packed_bytes(lay.PageCount_K, lay.PageCount_V)
+            attn_alg += B * attention_bytes(lay)
+            attn_ev[i][0].record()
+            kb.kitty_attention_forward(mod, q, lay, scaling)
+            attn_ev[i][1].record()
+            flush = lay.Q_Buffer_Count_K == 128 or lay.Q_Buffer_Count_V == 128
+            cache.quantize_decode(0)
+            launches["n"] += 4 + (1 if flush else 0)
+        ev1.record()
+        barrier()
+    ms = ev0.elapsed_time(ev1)
+    attn_ms = sum(a.elapsed_time(b) for a, b in attn_ev)
+    gpu_launches = launches["n"]
+    t = torch.tensor([ms, attn_ms], device=device, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, attn_ms = float(t[0]), float(t[1])
+    value = world * packed / (ms * 1e-3) / 1e9
+    tokens_per_s = world * B * K / (ms * 1e-3)
+
+    # ---------------- end-to-end pass: pinned host inputs, result copied back every step ---------------- #
+    hq = qs[W + K:].cpu().pin_memory()
+    hk = ks[W + K:].cpu().pin_memory()
+    hv = vs[W + K:].cpu().pin_memory()
+    hout = torch.empty(B, 1, H_Q, D, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step(i):
+        q = hq[i].to(device, non_blocking=True)
+        k = hk[i].to(device, non_blocking=True)
+        v = hv[i].to(device, non_blocking=True)
+        out = step(q, k, v)
+        hout.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()       # the caller reads the result of every step
+
+    for i in range(W):
+        e2e_step(i)
+    barrier()
+    packed_e = 0
+    t0 = time.perf_counter()
+    for i in range(K):
+        e2e_step(W + i)
+        packed_e += B * packed_bytes(lay.PageCount_K, lay.PageCount_V)
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    te = torch.tensor([e2e_s], device=device, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_s = float(te[0])
+    h2d = B * (H_Q + 2 * H_KV) * D * 2
+    d2h = B * H_Q * D * 2
+    from kitty_b200.attention import workspace_status
+
+    if workspace_status(lay) != 0:
+        raise SystemExit("device-side bounded wait ran out during the benchmark")
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = json.load(open(peaks_path))["hbm_gbs"], "measured (MEASURED_PEAKS.json hbm_gbs)"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+    achieved = (attn_alg / K) / (attn_ms / K * 1e-3) / 1e9     # per attention call, this rank
+    line = {
+        "metric": "decode_attn_packed_kv_throughput", "value": value, "unit": "GB/s", "n_gpus": world, "steps": K,
+        "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"decode step, 1 layer, 32q/8kv heads, head_dim 128, {args.ctx} cached tokens, bf16 q/k/v, "
+                               "2-bit K (25% channels 4-bit) / 2-bit V pages",
+                   "batch_per_gpu": B, "global_batch": B * world, "parallelism": f"batch-sharded x{world}, no collective",
+                   "l2": f"inputs larger than L2 ({B * packed_bytes(lay.PageCount_K, lay.PageCount_V) / 1e6:.0f} MB of packed pages per GPU per step)"},
+        "decode_tokens_per_s": tokens_per_s,
+        "e2e": {"value": world * packed_e / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s / K * 1e3, "decode_tokens_per_s": world * B * K / e2e_s},
+        "gpu_launches": gpu_launches,
+        "clocks": clocks.summary(),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_source": peak_src,
+                     "kernel": "decode attention call = decode_paged_kernel + decode_plain_kernel + merge_kernel "
+                               "(algorithmic bytes of the call / CUDA-event time of the call)",
+                     "algorithmic_bytes_per_call": attn_alg / K, "ms_per_call": attn_ms / K},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        r = cpu_reference(args.ctx, 40, 2, budget_s=20.0)
+        line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    if args.sweep and world == 1:
+        sweep = {}
+        for b in (1, 8, 32):
+            c2 = build_cache(kb, b, args.ctx, 64, device, seed=7)
+            l2 = c2.kv_cache[0]
+            q = torch.randn(b, H_Q, 1, D, device=device).to(torch.bfloat16)
+            c2.update(torch.randn(b, H_KV, 1, D, device=device).to(torch.bfloat16),
+                      torch.randn(b, H_KV, 1, D, device=device).to(torch.bfloat16), 0)
+            for _ in range(5):
+                kb.kitty_attention_forward(mod, q, l2, scaling)
+            a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+            tot = 0.0
+            for _ in range(20):
+                flush_buf.zero_()                      # evict the cache from L2 between iterations
+                a.record()
+                kb.kitty_attention_forward(mod, q, l2, scaling)
+                z.record()
+                z.synchronize()
+                tot += a.elapsed_time(z)
+            us = tot / 20 * 1e3
+            sweep[f"batch{b}"] = {"us_per_call": us, "GBps": b * attention_bytes(l2) / (us * 1e-6) / 1e9,
+                                  "frac_of_peak": b * attention_bytes(l2) / (us * 1e-6) / 1e9 / peak}
+            del c2, flush_buf
+        line["sweep_attention_call_l2_flushed"] = sweep
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,168 @@
+/*
+ * kitty_b200 — C ABI of the B200 (sm_100a) implementation of Kitty's quantized
+ * KV-cache hot path: quantize-and-append, flush, fused dequant decode attention.
+ *
+ * Every entry point takes plain pointers and sizes, launches on the CUDA stream
+ * it is given, never synchronises the host with the device, never allocates or
+ * frees device memory (unless its comment says otherwise) and returns an int:
+ * 0 on success, a negative kitty_status otherwise.  Nothing throws.
+ *
+ * File:line citations name the reference interface (paths inside the Kitty
+ * project, src/kitty/...) that the entry point replaces.
+ *
+ * Geometry is fixed to what the reference hard-codes (kvcache/kitty.py:43-47):
+ * page = 128 tokens, head_dim = 128, 32 boosted channels, sink = 32 tokens.
+ * Anything else is rejected with KITTY_E_BADSHAPE.
+ */
+#ifndef KITTY_B200_H
+#define KITTY_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  KITTY_OK = 0,
+  KITTY_E_BADARG = -1,    /* null / misaligned pointer, bad enum, negative count        */
+  KITTY_E_BADSHAPE = -2,  /* geometry other than page 128 / D 128 / 32 boosted / G > 16 */
+  KITTY_E_WORKSPACE = -3, /* caller's workspace too small                               */
+  KITTY_E_CUDA = -4,      /* a CUDA runtime call failed (see cudaGetLastError)          */
+  KITTY_E_TIMEOUT = -5    /* a bounded device-side wait ran out                         */
+} kitty_status;
+
+typedef enum { KITTY_F16 = 0, KITTY_BF16 = 1, KITTY_F32 = 2 } kitty_dtype;
+
+/* How the 32 boosted key channels of a page are chosen. */
+typedef enum {
+  /* In-kernel: score = mean|x| over the page rounded once to the input dtype,
+     descending, equal scores ordered by ascending channel number; slot = rank.
+     (kernels/kitty_quant_pack.py:280-288 with a defined tie order.) */
+  KITTY_SELECT_FUSED = 0,
+  /* The caller supplies the dense->sparse index bytes, as the reference's kernel
+     receives them (kernels/kitty_quant_pack.py:19-20, 65-71). */
+  KITTY_SELECT_SUPPLIED = 1
+} kitty_select_mode;
+
+/* fp32 division used for (x - min) / scale. */
+typedef enum {
+  KITTY_DIV_IEEE = 0, /* correctly rounded; equals the reference run on a host    */
+  KITTY_DIV_FULL = 1  /* PTX div.full.f32 (2 ulp)                                 */
+} kitty_div_mode;
+
+/* Device buffers of one layer, with the names, shapes and dtypes of the
+ * reference's KVCache_Layer (kvcache/utils_kv_per_layer.py:18-83).  All tensors
+ * are contiguous; strides that may differ are explicit. */
+typedef struct {
+  int32_t max_bs, max_page, h_kv, head_dim, d_boost, page_size, sink_size, reserved;
+  uint8_t *KeyCache;            /* u8  [max_bs*max_page, h_kv*5248]        */
+  void *KeyCache_metadata;      /* f16 [max_bs*max_page, h_kv, 128, 2]     */
+  uint8_t *ValueCache;          /* u8  [max_bs*max_page, h_kv*4096]        */
+  void *ValueCache_metadata;    /* f16 [max_bs*max_page, h_kv, 128, 2]     */
+  const int64_t *PageTable_K;   /* i64 [max_bs, max_page]                  */
+  const int64_t *PageTable_V;   /* i64 [max_bs, max_page]                  */
+  void *Sink_Buffer_K;          /* f16 [max_bs, h_kv, 32, 128]             */
+  void *Sink_Buffer_V;
+  void *Q_Buffer_K;             /* f16 [max_bs, h_kv, 128, 128]            */
+  void *Q_Buffer_V;
+  void *Local_Buffer_V;         /* f16 [max_bs, h_kv, 128, 128] ring       */
+} kitty_layer;
+
+/* The reference keeps these as Python ints on the layer object
+ * (utils_kv_per_layer.py:53-80) and passes them to its kernels as scalars. */
+typedef struct {
+  int32_t PageCount_K, PageCount_V, Sink_Count, Q_Buffer_Count_K, Q_Buffer_Count_V, Local_Count_V,
+      Write_Offset_Local_V, reserved;
+} kitty_counts;
+
+int kitty_version(void);
+const char *kitty_strerror(int status);
+
+/* quantize_pack_k (kernels/kitty_quant_pack.py:253-312 and the kernel at :13-152).
+ * key: [B, H, T, 128] of `dtype`, element strides (stride_b, stride_h, stride_t), unit
+ * stride over channels, every row 16-byte aligned.  Quantizes tokens
+ * [t_offset, t_offset + 128*pages) of every (b, h) into pages
+ * page_table[b, page_offset + p].  idx_io: u8 [B, H, pages, 128], read when
+ * select == KITTY_SELECT_SUPPLIED, written (if non-null) with the chosen bytes
+ * otherwise.  One pass over the keys: score, top-32 rank, min/max, codes, pack. */
+int kitty_quant_pack_k(const void *key, int dtype, int64_t stride_b, int64_t stride_h, int64_t stride_t,
+                       int32_t B, int32_t H, int64_t t_offset, int32_t pages, const int64_t *page_table,
+                       int64_t page_table_stride_b, int32_t page_offset, uint8_t *cache,
+                       int64_t cache_stride_page, void *cache_meta, uint8_t *idx_io, int select, int div_mode,
+                       void *stream);
+
+/* quantize_pack_v (kernels/kitty_quant_pack.py:315-356, kernel at :155-249). */
+int kitty_quant_pack_v(const void *value, int dtype, int64_t stride_b, int64_t stride_h, int64_t stride_t,
+                       int32_t B, int32_t H, int64_t t_offset, int32_t pages, const int64_t *page_table,
+                       int64_t page_table_stride_b, int32_t page_offset, uint8_t *cache,
+                       int64_t cache_stride_page, void *cache_meta, int div_mode, void *stream);
+
+/* The full-precision copies of KittyCache.quantize_prefill (kvcache/kitty.py:137-141,
+ * 164-172) in one launch: the first `sink` tokens into the sink buffers, the last
+ * qbuf_k keys into Q_Buffer_K, the last local_v values into Local_Buffer_V and the
+ * qbuf_v values before those into Q_Buffer_V, all cast to fp16.  key/value:
+ * [B, H, L, 128] with the given element strides. */
+int kitty_prefill_tails(const kitty_layer *layer, const void *key, const void *value, int dtype,
+                        int64_t k_stride_b, int64_t k_stride_h, int64_t k_stride_t, int64_t v_stride_b,
+                        int64_t v_stride_h, int64_t v_stride_t, int32_t B, int64_t L, int32_t sink,
+                        int32_t qbuf_k, int32_t local_v, int32_t qbuf_v, void *stream);
+
+/* Decode branch of KittyCache.update (kvcache/kitty.py:101-123): one token per
+ * (b, h) goes to the sink, or to Q_Buffer_K and the value ring (the ring's oldest
+ * token moving to Q_Buffer_V when the ring is full).  `counts` is the state
+ * BEFORE the append; the caller advances its counters exactly as kitty.py does.
+ * key/value: [B, H, 1, 128] with element strides (stride_b, stride_h). */
+int kitty_append(const kitty_layer *layer, const kitty_counts *counts, const void *key, const void *value,
+                 int dtype, int64_t k_stride_b, int64_t k_stride_h, int64_t v_stride_b, int64_t v_stride_h,
+                 int32_t B, void *stream);
+
+/* KittyCache.quantize_decode (kvcache/kitty.py:194-236): Q_Buffer_K becomes key
+ * page PageCount_K when flush_k != 0 and Q_Buffer_V becomes value page
+ * PageCount_V when flush_v != 0 — both in one launch. */
+int kitty_flush(const kitty_layer *layer, const kitty_counts *counts, int32_t B, int flush_k, int flush_v,
+                int select, int div_mode, void *stream);
+
+/* Bytes of scratch kitty_decode_attn needs for this problem size (negative
+ * kitty_status on bad arguments).  The workspace is caller-owned device memory,
+ * 256-byte aligned, ZERO-FILLED ONCE before its first use: its first word is a
+ * sticky status that a kernel sets when a bounded wait runs out.  Calls that
+ * share a workspace must not overlap on the device.  The reference allocates its
+ * scratch (the logits tensor) inside the call (kernels/kitty_attention.py:426-430). */
+int64_t kitty_decode_workspace_bytes(int32_t B, int32_t h_kv, int32_t h_q, int32_t max_pages);
+
+/* Copies the workspace's status word to *host_status and SYNCHRONISES the stream
+ * (the one entry point that does).  Returns KITTY_E_TIMEOUT when it is set. */
+int kitty_workspace_status(const void *workspace, int32_t *host_status, void *stream);
+
+/* kitty_attention_forward (kernels/kitty_attention.py:403-526: qk_kernel, softmax,
+ * sv_kernel) as one fused pass: split over the sequence, online softmax, packed
+ * pages streamed with bulk async copies and unpacked in registers.
+ * query: [B, h_q, 1, 128] contiguous of q_dtype (F16 or BF16, F32 accepted).
+ * out:   [B, 1, h_q, 128] contiguous of out_dtype.
+ * page_begin/page_end restrict the packed pages visited (sequence split across
+ * GPUs); pass 0 and -1 for all pages.  flags: bit0 include the sink tokens, bit1
+ * include everything after the last common packed page (extra key pages,
+ * Q-buffers, value ring); pass 3 on a single GPU.
+ * If partial_out is non-null the un-normalised result is written there instead
+ * of `out`, as fp32 [B, h_q, 130] = (acc[128], running max, running sum) in the
+ * base-2 domain, for kitty_lse_merge.
+ * impl: 0 = default kernels; 1 = the plain CUDA-core kernel for every tile
+ * (slow; kept as an in-library cross-check). */
+int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *counts, const void *query, int q_dtype,
+                      int32_t B, int32_t h_q, float scaling, void *out, int out_dtype, void *workspace,
+                      int64_t workspace_bytes, int32_t page_begin, int32_t page_end, int32_t flags,
+                      float *partial_out, int impl, void *stream);
+
+/* Log-sum-exp combination of n_parts partial results (fp32 [n_parts, rows, 130],
+ * the layout partial_out uses; rows = B*h_q) into out [rows, 128] of out_dtype.
+ * Used after the all-gather of a sequence-split decode step.  The reference has
+ * no multi-GPU path (utils_kv_per_layer.py:16 "To Do: Multi-GPU Inference"). */
+int kitty_lse_merge(const float *partials, int32_t n_parts, int64_t rows, void *out, int out_dtype,
+                    void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KITTY_B200_H */

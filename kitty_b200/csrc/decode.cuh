@@ -1,0 +1,65 @@
+// Work decomposition shared by the decode-attention kernels.
+//
+// Token order of one (batch, kv-head) sequence (kernels/kitty_attention.py:88-207,
+// 269-386 of the reference):
+//   keys   = sink | packed key pages   | Q_Buffer_K
+//   values = sink | packed value pages | Q_Buffer_V | ring (oldest first)
+// "Tile" u = 0 is the sink; tile u >= 1 covers positions [(u-1)*128, u*128) after
+// the sink.  Tiles 1..PageCount_V hold a packed key page AND a packed value page
+// ("common pages", the streaming hot loop); later tiles pair extra key pages or
+// Q_Buffer_K with fp16 values ("tail").
+//
+// A decode call is cut into items; each item reduces a run of tiles for one
+// (batch, kv-head) to a partial result (acc[128], max, sum) per query head in
+// the workspace, and a merge kernel combines the slots.
+#pragma once
+
+#include "common.cuh"
+
+namespace kitty {
+
+struct DecodePlan {
+  int32_t B, H, G, h_q;
+  int32_t pb, pe;        // common pages visited: [pb, pe), pe <= PageCount_V
+  int32_t ch;            // pages per chunk
+  int32_t nchunk;        // chunks per (b, h)
+  int32_t has_sink;      // slot 0 is the sink tile
+  int32_t has_tail;      // last slot is the tail
+  int32_t n_slots;       // has_sink + nchunk + has_tail
+  int32_t n_tiles;       // total tiles of the sequence (sink tile included)
+  int32_t fast_chunks;   // 1: chunks are reduced by the streaming kernel, 0: by the plain kernel
+};
+
+struct DecodeArgs {
+  kitty_layer L;
+  kitty_counts C;
+  DecodePlan P;
+  const void *q;         // [B, h_q, 1, 128]
+  int32_t q_dtype;
+  float scale_log2;      // scaling * log2(e): logits live in the base-2 domain
+  float *partials;       // [B*H, n_slots, G, PART]
+  int32_t *status;       // device word, set non-zero when a bounded wait ran out
+};
+
+// Merge n partials per row.  Row r's partial s lives at
+//   base + ((r / gm) * ns * gm + r % gm) * PART + s * stride_part   (floats).
+struct MergeArgs {
+  const float *partials;
+  int64_t rows, stride_part;
+  int32_t n, gm, ns;
+  void *out;          // [rows, 128] of out_dtype, or null
+  int32_t out_dtype;
+  float *partial_out; // [rows, PART] or null: merged but un-normalised
+};
+
+int launch_decode_plain(const DecodeArgs &a, int items_per_bh, cudaStream_t s);
+int launch_decode_paged(const DecodeArgs &a, int n_items, int n_gt, int grid, cudaStream_t s);
+int launch_merge(const MergeArgs &m, cudaStream_t s);
+
+__device__ __forceinline__ float load_q(const void *q, int dtype, int64_t i) {
+  if (dtype == KITTY_F16) return __half2float(static_cast<const __half *>(q)[i]);
+  if (dtype == KITTY_BF16) return __bfloat162float(static_cast<const __nv_bfloat16 *>(q)[i]);
+  return static_cast<const float *>(q)[i];
+}
+
+}  // namespace kitty

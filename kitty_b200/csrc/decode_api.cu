@@ -1,0 +1,186 @@
+// Host side of the decode-attention entry points: argument checks, the split of
+// a call into items (chunks of common pages, the sink tile, the tail) and the
+// launches.  No allocation, no host/device synchronisation.
+#include <algorithm>
+
+#include "decode.cuh"
+
+namespace kitty {
+
+constexpr int64_t WS_HEADER = 256;   // bytes at the start of the workspace: sticky status word
+constexpr int PG_WARPS_HOST = 4;     // warps per block of the streaming kernel (pages per chunk come in multiples)
+
+static int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+static int chunk_cap(int64_t bh_gt, int grid_max) {
+  const int64_t cap = (16LL * grid_max) / std::max<int64_t>(1, bh_gt);
+  return static_cast<int>(std::min<int64_t>(64, std::max<int64_t>(1, cap)));
+}
+
+// Pick pages-per-chunk so that the items fill `grid_max` resident blocks in whole waves.
+static void plan_chunks(int n_pages, int64_t bh_gt, int grid_max, int *ch_out, int *nchunk_out) {
+  if (n_pages <= 0) {
+    *ch_out = PG_WARPS_HOST;
+    *nchunk_out = 0;
+    return;
+  }
+  const int cap = std::min(chunk_cap(bh_gt, grid_max), (n_pages + PG_WARPS_HOST - 1) / PG_WARPS_HOST);
+  double best = 1e30;
+  int best_ch = n_pages, best_n = 1;
+  for (int want = 1; want <= cap; ++want) {
+    int ch = (n_pages + want - 1) / want;
+    ch = (ch + PG_WARPS_HOST - 1) / PG_WARPS_HOST * PG_WARPS_HOST;
+    const int n = (n_pages + ch - 1) / ch;
+    const int64_t items = bh_gt * n;
+    const int64_t waves = (items + grid_max - 1) / grid_max;
+    const double cost = static_cast<double>(waves) * (ch / PG_WARPS_HOST + 1.5);   // +1.5: per-item prologue/merge
+    if (cost < best - 1e-9) {
+      best = cost;
+      best_ch = ch;
+      best_n = n;
+    }
+  }
+  *ch_out = best_ch;
+  *nchunk_out = best_n;
+}
+
+}  // namespace kitty
+
+using namespace kitty;
+
+extern "C" int64_t kitty_decode_workspace_bytes(int32_t B, int32_t h_kv, int32_t h_q, int32_t max_pages) {
+  if (B <= 0 || h_kv <= 0 || h_q <= 0 || h_q % h_kv != 0 || max_pages < 0) return KITTY_E_BADARG;
+  const int G = h_q / h_kv;
+  if (G > MAX_GROUP) return KITTY_E_BADSHAPE;
+  const int n_gt = (G + 7) / 8;
+  const int grid_max = 2 * sm_count();
+  const int64_t bh = static_cast<int64_t>(B) * h_kv;
+  int cap = chunk_cap(bh * n_gt, grid_max);
+  cap = std::min(cap, std::max(1, (max_pages + PG_WARPS_HOST - 1) / PG_WARPS_HOST));
+  return WS_HEADER + bh * (cap + 2) * G * PART * static_cast<int64_t>(sizeof(float));
+}
+
+extern "C" int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *counts, const void *query, int q_dtype,
+                                 int32_t B, int32_t h_q, float scaling, void *out, int out_dtype, void *workspace,
+                                 int64_t workspace_bytes, int32_t page_begin, int32_t page_end, int32_t flags,
+                                 float *partial_out, int impl, void *stream) {
+  if (!layer || !counts || !query || !workspace) return KITTY_E_BADARG;
+  if (!out && !partial_out) return KITTY_E_BADARG;
+  if (layer->head_dim != HD || layer->page_size != PAGE || layer->d_boost != DB || layer->sink_size != SINK)
+    return KITTY_E_BADSHAPE;
+  const int H = layer->h_kv;
+  if (B <= 0 || B > layer->max_bs || H <= 0 || h_q <= 0 || h_q % H != 0) return KITTY_E_BADARG;
+  const int G = h_q / H;
+  if (G > MAX_GROUP) return KITTY_E_BADSHAPE;
+  if (q_dtype < KITTY_F16 || q_dtype > KITTY_F32 || out_dtype < KITTY_F16 || out_dtype > KITTY_F32) return KITTY_E_BADARG;
+  if (impl != 0 && impl != 1) return KITTY_E_BADARG;
+  if (B > 65535 || H > 65535) return KITTY_E_BADARG;
+  const kitty_counts &C = *counts;
+  if (C.PageCount_K < 0 || C.PageCount_V < 0 || C.PageCount_K > layer->max_page || C.PageCount_V > layer->max_page ||
+      C.Sink_Count < 0 || C.Sink_Count > SINK || C.Q_Buffer_Count_K < 0 || C.Q_Buffer_Count_K > PAGE ||
+      C.Q_Buffer_Count_V < 0 || C.Q_Buffer_Count_V > PAGE || C.Local_Count_V < 0 || C.Local_Count_V > PAGE ||
+      C.Write_Offset_Local_V < 0 || C.Write_Offset_Local_V >= PAGE)
+    return KITTY_E_BADARG;
+  const int64_t tk = static_cast<int64_t>(C.PageCount_K) * PAGE + C.Q_Buffer_Count_K;
+  const int64_t tv = static_cast<int64_t>(C.PageCount_V) * PAGE + C.Q_Buffer_Count_V + C.Local_Count_V;
+  if (tk != tv || C.PageCount_V > C.PageCount_K) return KITTY_E_BADARG;          // utils_kv_per_layer.py:94
+  if (C.Sink_Count < SINK && tk != 0) return KITTY_E_BADARG;                      // pages exist only once the sink is full
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return KITTY_E_BADARG;
+
+  DecodeArgs a;
+  a.L = *layer;
+  a.C = C;
+  DecodePlan &P = a.P;
+  P.B = B; P.H = H; P.G = G; P.h_q = h_q;
+  const int pv = C.PageCount_V;
+  P.pb = std::min(std::max(page_begin, 0), pv);
+  P.pe = page_end < 0 ? pv : std::min(std::max(page_end, P.pb), pv);
+  P.n_tiles = 1 + static_cast<int>((tk + PAGE - 1) / PAGE);
+  P.has_sink = ((flags & 1) && C.Sink_Count > 0) ? 1 : 0;
+  P.has_tail = ((flags & 2) && (P.n_tiles - 1 - pv) > 0) ? 1 : 0;
+  const int n_gt = (G + 7) / 8;
+  const int grid_max = 2 * sm_count();
+  plan_chunks(P.pe - P.pb, static_cast<int64_t>(B) * H * n_gt, grid_max, &P.ch, &P.nchunk);
+  P.n_slots = P.has_sink + P.nchunk + P.has_tail;
+  P.fast_chunks = (impl == 0) ? 1 : 0;
+  if (P.n_slots == 0 && !partial_out) return KITTY_E_BADARG;                      // nothing to attend to
+
+  const int64_t need = WS_HEADER + static_cast<int64_t>(B) * H * P.n_slots * G * PART * static_cast<int64_t>(sizeof(float));
+  if (workspace_bytes < need) return KITTY_E_WORKSPACE;
+  a.q = query;
+  a.q_dtype = q_dtype;
+  a.scale_log2 = scaling * 1.4426950408889634f;
+  a.status = static_cast<int32_t *>(workspace);
+  a.partials = reinterpret_cast<float *>(static_cast<uint8_t *>(workspace) + WS_HEADER);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  if (P.fast_chunks && P.nchunk > 0) {
+    const int64_t items = static_cast<int64_t>(B) * H * n_gt * P.nchunk;
+    const int grid = static_cast<int>(std::min<int64_t>(items, grid_max));
+    if (int rc = launch_decode_paged(a, static_cast<int>(items), n_gt, grid, s)) return rc;
+  }
+  const int plain_items = P.has_sink + (P.fast_chunks ? 0 : P.nchunk) + P.has_tail;
+  if (plain_items > 0)
+    if (int rc = launch_decode_plain(a, plain_items, s)) return rc;
+
+  MergeArgs m;
+  m.partials = a.partials;
+  m.rows = static_cast<int64_t>(B) * h_q;
+  m.stride_part = static_cast<int64_t>(G) * PART;
+  m.n = P.n_slots;
+  m.gm = G;
+  m.ns = P.n_slots;
+  m.out = out;
+  m.out_dtype = out_dtype;
+  m.partial_out = partial_out;
+  return launch_merge(m, s);
+}
+
+extern "C" int kitty_lse_merge(const float *partials, int32_t n_parts, int64_t rows, void *out, int out_dtype,
+                               void *stream) {
+  if (!partials || !out || n_parts <= 0 || rows < 0) return KITTY_E_BADARG;
+  if (out_dtype < KITTY_F16 || out_dtype > KITTY_F32) return KITTY_E_BADARG;
+  MergeArgs m;
+  m.partials = partials;
+  m.rows = rows;
+  m.stride_part = rows * PART;
+  m.n = n_parts;
+  m.gm = 1;
+  m.ns = 1;
+  m.out = out;
+  m.out_dtype = out_dtype;
+  m.partial_out = nullptr;
+  return launch_merge(m, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int kitty_workspace_status(const void *workspace, int32_t *host_status, void *stream) {
+  if (!workspace || !host_status) return KITTY_E_BADARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMemcpyAsync(host_status, workspace, sizeof(int32_t), cudaMemcpyDeviceToHost, s) != cudaSuccess) return KITTY_E_CUDA;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return KITTY_E_CUDA;
+  return *host_status ? KITTY_E_TIMEOUT : KITTY_OK;
+}
+
+extern "C" int kitty_version(void) { return 100; }
+
+extern "C" const char *kitty_strerror(int status) {
+  switch (status) {
+    case KITTY_OK: return "ok";
+    case KITTY_E_BADARG: return "bad argument (null or misaligned pointer, bad enum, inconsistent counters)";
+    case KITTY_E_BADSHAPE: return "unsupported geometry (need page 128, head_dim 128, 32 boosted channels, sink 32, group <= 16)";
+    case KITTY_E_WORKSPACE: return "workspace too small (see kitty_decode_workspace_bytes)";
+    case KITTY_E_CUDA: return "CUDA runtime error";
+    case KITTY_E_TIMEOUT: return "a bounded device-side wait ran out";
+    default: return "unknown status";
+  }
+}

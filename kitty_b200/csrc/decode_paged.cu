@@ -1,0 +1,434 @@
+// Streaming decode attention over the common packed pages (key page i and
+// value page i of one (batch, kv-head)), the hot loop of the decode step.
+//
+// Data path.  Each warp owns a private ring of shared-memory stages.  One lane
+// issues four bulk async copies (cp.async.bulk, completion counted on an
+// mbarrier) per page pair: key record 5248 B, key metadata 512 B, value record
+// 4096 B, value metadata 512 B — the 10368 algorithmic bytes of the pair, each
+// fetched from HBM exactly once.  While a pair is being reduced the next one is
+// in flight.
+//
+// Arithmetic.  The 2-bit fields are never expanded one by one.  A 32-bit word of
+// the record holds 16 tokens (keys) or 16 channels (values); two such words are
+// byte-permuted into a register whose 16-bit halves hold the same field
+// positions of two contraction indices, and `word & (3 << 2f)` IS an fp16x2
+// operand: an fp16 subnormal whose value is code * 4^f * 2^-24.  mma.sync
+// m16n8k16 (tokens or channels on M, the grouped query heads on N = 8) consumes
+// it directly; the power-of-two row factor is applied to the fp32 accumulators.
+// Scales are folded into the small operand (q*scale per page for keys, p*scale
+// per token for values); the `+ min` terms are rank-1 and are produced by one
+// extra mma chain each (rows of min / zero-point against q / p), the value
+// chain also yielding the softmax denominator from a row of ones.
+//
+// Per (page pair, warp): 160 mma.sync, ~1.2 k other instructions.
+#include "decode.cuh"
+
+namespace kitty {
+
+constexpr int PG_WARPS = 4;
+constexpr int PG_STAGES = 2;
+constexpr int OFF_KREC = 0;
+constexpr int OFF_KMETA = K_HEAD;                   // 5248
+constexpr int OFF_VREC = OFF_KMETA + META_HEAD;     // 5760
+constexpr int OFF_VMETA = OFF_VREC + V_HEAD;        // 9856
+constexpr int STAGE_BYTES = OFF_VMETA + META_HEAD;  // 10368
+constexpr int PB_ROW = 68;                          // words per query-head row of the probability buffer (64 + pad)
+constexpr int PB_WORDS = 8 * PB_ROW;
+constexpr int QS_ROW = HD + 8;                      // halves per row of the staged query
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+struct PagedSmem {
+  __align__(128) uint8_t stage[PG_WARPS][PG_STAGES][STAGE_BYTES];
+  __align__(16) uint32_t pbuf[PG_WARPS][PB_WORDS];
+  __align__(16) __half qs[8][QS_ROW];
+  __align__(8) unsigned long long bar[PG_WARPS][PG_STAGES];
+  uint8_t inv[PG_WARPS][DB];
+};
+static_assert(PG_WARPS * 8 * PART * 4 <= PG_WARPS * PG_STAGES * STAGE_BYTES, "merge buffer overlays the stages");
+
+// ---- PTX wrappers --------------------------------------------------------- //
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the copy did not land within the limit.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t hmul2_u(uint32_t a, uint32_t b) {
+  __half2 r = __hmul2(*reinterpret_cast<__half2 *>(&a), *reinterpret_cast<__half2 *>(&b));
+  return *reinterpret_cast<uint32_t *>(&r);
+}
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+  __half2 r = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&r);
+}
+
+// Field f (0..7) of both 16-bit halves of x as an fp16x2 operand, and the power
+// of two that undoes its weight.  Fields 5..7 sit in the exponent bits, so they
+// are taken from the copy shifted right by 10 (xs), where they are fields 0..2.
+__device__ __forceinline__ uint32_t field(uint32_t x, uint32_t xs, int f) {
+  return (f < 5) ? (x & (0x00030003u << (2 * f))) : (xs & (0x00030003u << (2 * (f - 5))));
+}
+__host__ __device__ constexpr float field_unscale(int f) {
+  // 2^24 / 4^pos, pos = f for f < 5 and f - 5 otherwise
+  return 16777216.0f / static_cast<float>(1 << (2 * (f < 5 ? f : f - 5)));
+}
+
+struct PairSrc {
+  const uint8_t *krec, *kmeta, *vrec, *vmeta;
+};
+
+__device__ __forceinline__ PairSrc pair_src(const DecodeArgs &a, int b, int h, int page) {
+  const int H = a.P.H;
+  const int64_t pk = a.L.PageTable_K[static_cast<int64_t>(b) * a.L.max_page + page];
+  const int64_t pv = a.L.PageTable_V[static_cast<int64_t>(b) * a.L.max_page + page];
+  PairSrc s;
+  s.krec = a.L.KeyCache + pk * (static_cast<int64_t>(H) * K_HEAD) + static_cast<int64_t>(h) * K_HEAD;
+  s.kmeta = static_cast<const uint8_t *>(a.L.KeyCache_metadata) + (pk * H + h) * META_HEAD;
+  s.vrec = a.L.ValueCache + pv * (static_cast<int64_t>(H) * V_HEAD) + static_cast<int64_t>(h) * V_HEAD;
+  s.vmeta = static_cast<const uint8_t *>(a.L.ValueCache_metadata) + (pv * H + h) * META_HEAD;
+  return s;
+}
+
+__global__ void __launch_bounds__(PG_WARPS * 32) decode_paged_kernel(DecodeArgs a, int n_items, int n_gt) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  PagedSmem &sm = *reinterpret_cast<PagedSmem *>(smem_raw);
+  const DecodePlan &P = a.P;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int gid = lane >> 2, tig = lane & 3;
+  const int H = P.H, G = P.G;
+
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < PG_STAGES; ++s) mbar_init(smem_u32(&sm.bar[warp][s]), 1);
+  }
+  if (lane < DB) sm.inv[warp][lane] = 0;
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  __syncthreads();
+
+  uint32_t seq = 0;          // page pairs consumed by this warp so far (ring position and parity)
+  bool dead = false;         // a bounded wait ran out: stop consuming, keep the barriers uniform
+  uint32_t inflight = 0;     // bit s: stage s has a copy in flight (lane 0's view, kept warp-uniform)
+
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const int c = item % P.nchunk;
+    const int gt = (item / P.nchunk) % n_gt;
+    const int bh = item / (P.nchunk * n_gt);
+    const int h = bh % H, b = bh / H;
+    const int p0 = P.pb + c * P.ch;
+    const int p1 = min(P.pe, p0 + P.ch);
+    const int g_valid = min(8, G - gt * 8);
+
+    __syncthreads();   // previous item's merge buffer (overlaying the stages) and query are no longer read
+    for (int i = tid; i < 8 * HD; i += PG_WARPS * 32) {
+      const int g = i >> 7, d = i & (HD - 1);
+      float v = 0.f;
+      if (g < g_valid) v = load_q(a.q, a.q_dtype, (static_cast<int64_t>(b) * P.h_q + h * G + gt * 8 + g) * HD + d) * a.scale_log2;
+      sm.qs[g][d] = __float2half_rn(v);
+    }
+    // first copies of this warp: pages p0 + warp, p0 + warp + PG_WARPS, ...
+    const int first = p0 + warp;
+    if (lane == 0 && !dead) {
+      // the stages were last written through the generic proxy (merge buffer); order that before the bulk copies
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#pragma unroll
+      for (int s = 0; s < PG_STAGES; ++s) {
+        const int pg = first + s * PG_WARPS;
+        if (pg < p1) {
+          const uint32_t st = (seq + s) % PG_STAGES;
+          const uint32_t bar = smem_u32(&sm.bar[warp][st]);
+          const uint32_t dst = smem_u32(&sm.stage[warp][st][0]);
+          const PairSrc src = pair_src(a, b, h, pg);
+          mbar_expect_tx(bar, STAGE_BYTES);
+          bulk_g2s(dst + OFF_KREC, src.krec, K_HEAD, bar);
+          bulk_g2s(dst + OFF_KMETA, src.kmeta, META_HEAD, bar);
+          bulk_g2s(dst + OFF_VREC, src.vrec, V_HEAD, bar);
+          bulk_g2s(dst + OFF_VMETA, src.vmeta, META_HEAD, bar);
+          inflight |= 1u << st;
+        }
+      }
+    }
+    inflight = __shfl_sync(0xffffffffu, inflight, 0);
+    __syncthreads();   // staged query visible
+
+    // query fragments: B operand column n = gid (query head), contraction index
+    // k = 2*tig, 2*tig+1, 2*tig+8, 2*tig+9  <->  channels 16*ks + tig + {0, 4, 8, 12}
+    uint32_t q2[8][2];
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const __half *qr = &sm.qs[gid][16 * ks + tig];
+      __half2 x = __halves2half2(qr[0], qr[4]);
+      __half2 y = __halves2half2(qr[8], qr[12]);
+      q2[ks][0] = *reinterpret_cast<uint32_t *>(&x);
+      q2[ks][1] = *reinterpret_cast<uint32_t *>(&y);
+    }
+
+    float acc[8][4];       // out[channel 16*gid + m (+8)][head 2*tig (+1)], still carrying the field weight
+    float cz[4] = {0.f, 0.f, 0.f, 0.f};   // [0,1]: sum p*zero-point, [2,3]: sum p, heads 2*tig, 2*tig+1
+#pragma unroll
+    for (int m = 0; m < 8; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
+    float m_run0 = -INFINITY, m_run1 = -INFINITY;
+
+    for (int pg = first; pg < p1; pg += PG_WARPS) {
+      if (dead) break;
+      const uint32_t st = seq % PG_STAGES, parity = (seq / PG_STAGES) & 1u;
+      const uint32_t bar = smem_u32(&sm.bar[warp][st]);
+      if (!mbar_wait(bar, parity)) {
+        dead = true;
+        if (lane == 0) atomicExch(a.status, 1);
+        break;
+      }
+      inflight &= ~(1u << st);
+      const uint8_t *stg = sm.stage[warp][st];
+      const uint32_t *kw = reinterpret_cast<const uint32_t *>(stg + OFF_KREC);
+      const uint32_t *hw = reinterpret_cast<const uint32_t *>(stg + OFF_KREC + K_OFF_HI);
+      const uint32_t *km = reinterpret_cast<const uint32_t *>(stg + OFF_KMETA);
+      const uint32_t *vw = reinterpret_cast<const uint32_t *>(stg + OFF_VREC);
+      const uint32_t *vm = reinterpret_cast<const uint32_t *>(stg + OFF_VMETA);
+
+      // slot -> channel table of this page
+      {
+        const uint32_t w = *reinterpret_cast<const uint32_t *>(stg + OFF_KREC + K_OFF_IDX + 4 * lane);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t s = (w >> (8 * i)) & 0xffu;
+          if (s < DB) sm.inv[warp][s] = static_cast<uint8_t>(4 * lane + i);
+        }
+      }
+
+      // ================= Q K^T ================= //
+      float cl[8][4];    // logits[token 16*gid + m (+8)][head 2*tig (+1)], carrying the field weight
+      float cb[4] = {0.f, 0.f, 0.f, 0.f};   // sum_d q*min, identical in every row
+#pragma unroll
+      for (int m = 0; m < 8; ++m) cl[m][0] = cl[m][1] = cl[m][2] = cl[m][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const int ch = 16 * ks + tig;
+        const uint32_t m0 = km[ch], m1 = km[ch + 4], m2 = km[ch + 8], m3 = km[ch + 12];   // (scale | min << 16)
+        const uint32_t b0 = hmul2_u(q2[ks][0], __byte_perm(m0, m1, 0x5410));
+        const uint32_t b1 = hmul2_u(q2[ks][1], __byte_perm(m2, m3, 0x5410));
+        const uint32_t mnA = __byte_perm(m0, m1, 0x7632), mnB = __byte_perm(m2, m3, 0x7632);
+        mma16816(cb, mnA, mnA, mnB, mnB, q2[ks][0], q2[ks][1]);
+        const uint32_t w0 = kw[ch * 8 + gid], w1 = kw[(ch + 4) * 8 + gid], w2 = kw[(ch + 8) * 8 + gid],
+                       w3 = kw[(ch + 12) * 8 + gid];
+        const uint32_t xab = __byte_perm(w0, w1, 0x5410), yab = __byte_perm(w0, w1, 0x7632);
+        const uint32_t xcd = __byte_perm(w2, w3, 0x5410), ycd = __byte_perm(w2, w3, 0x7632);
+        const uint32_t xabs = xab >> 10, yabs = yab >> 10, xcds = xcd >> 10, ycds = ycd >> 10;
+#pragma unroll
+        for (int m = 0; m < 8; ++m)
+          mma16816(cl[m], field(xab, xabs, m), field(yab, yabs, m), field(xcd, xcds, m), field(ycd, ycds, m), b0, b1);
+      }
+      __syncwarp();      // slot table complete
+      // high plane: contraction over slots 16*hs + tig + {0,4,8,12}; operand = 4 * q * scale of the slot's channel
+#pragma unroll
+      for (int hs = 0; hs < 2; ++hs) {
+        const int sl = 16 * hs + tig;
+        uint32_t bq[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int ca = sm.inv[warp][sl + 8 * j], cb2 = sm.inv[warp][sl + 8 * j + 4];
+          const __half2 qq = __halves2half2(sm.qs[gid][ca], sm.qs[gid][cb2]);
+          const __half2 ss = __halves2half2(__ushort_as_half(static_cast<unsigned short>(km[ca] & 0xffffu)),
+                                            __ushort_as_half(static_cast<unsigned short>(km[cb2] & 0xffffu)));
+          const __half2 r = __hmul2(__hmul2(qq, ss), __float2half2_rn(4.0f));
+          bq[j] = *reinterpret_cast<const uint32_t *>(&r);
+        }
+        const uint32_t w0 = hw[sl * 8 + gid], w1 = hw[(sl + 4) * 8 + gid], w2 = hw[(sl + 8) * 8 + gid],
+                       w3 = hw[(sl + 12) * 8 + gid];
+        const uint32_t xab = __byte_perm(w0, w1, 0x5410), yab = __byte_perm(w0, w1, 0x7632);
+        const uint32_t xcd = __byte_perm(w2, w3, 0x5410), ycd = __byte_perm(w2, w3, 0x7632);
+        const uint32_t xabs = xab >> 10, yabs = yab >> 10, xcds = xcd >> 10, ycds = ycd >> 10;
+#pragma unroll
+        for (int m = 0; m < 8; ++m)
+          mma16816(cl[m], field(xab, xabs, m), field(yab, yabs, m), field(xcd, xcds, m), field(ycd, ycds, m), bq[0], bq[1]);
+      }
+
+      // ================= online softmax ================= //
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int m = 0; m < 8; ++m) {
+        const float u = field_unscale(m);
+        cl[m][0] = fmaf(cl[m][0], u, cb[0]);
+        cl[m][1] = fmaf(cl[m][1], u, cb[1]);
+        cl[m][2] = fmaf(cl[m][2], u, cb[2]);
+        cl[m][3] = fmaf(cl[m][3], u, cb[3]);
+        mx0 = fmaxf(mx0, fmaxf(cl[m][0], cl[m][2]));
+        mx1 = fmaxf(mx1, fmaxf(cl[m][1], cl[m][3]));
+      }
+#pragma unroll
+      for (int o = 4; o < 32; o <<= 1) {
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+      }
+      const float mn0 = fmaxf(m_run0, mx0), mn1 = fmaxf(m_run1, mx1);
+      if (__any_sync(0xffffffffu, (mn0 > m_run0) || (mn1 > m_run1))) {
+        const float a0 = (m_run0 == -INFINITY) ? 0.f : ex2(m_run0 - mn0);
+        const float a1 = (m_run1 == -INFINITY) ? 0.f : ex2(m_run1 - mn1);
+#pragma unroll
+        for (int m = 0; m < 8; ++m) {
+          acc[m][0] *= a0; acc[m][1] *= a1; acc[m][2] *= a0; acc[m][3] *= a1;
+        }
+        cz[0] *= a0; cz[1] *= a1; cz[2] *= a0; cz[3] *= a1;
+        m_run0 = mn0;
+        m_run1 = mn1;
+      }
+      // probabilities, as fp16 pairs (token 16*gid + m, token 16*gid + 8 + m), into the warp's buffer
+      {
+        uint32_t pw[2][8];
+#pragma unroll
+        for (int m = 0; m < 8; ++m) {
+          const int pos = (m & 3) * 2 + (m >> 2);
+          pw[0][pos] = pack_h2(ex2(cl[m][0] - m_run0), ex2(cl[m][2] - m_run0));
+          pw[1][pos] = pack_h2(ex2(cl[m][1] - m_run1), ex2(cl[m][3] - m_run1));
+        }
+        uint32_t *pb = sm.pbuf[warp];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          uint4 *dst = reinterpret_cast<uint4 *>(pb + (2 * tig + j) * PB_ROW + gid * 8);
+          dst[0] = make_uint4(pw[j][0], pw[j][1], pw[j][2], pw[j][3]);
+          dst[1] = make_uint4(pw[j][4], pw[j][5], pw[j][6], pw[j][7]);
+        }
+      }
+      __syncwarp();
+
+      // ================= P V ================= //
+      // contraction index k = 2*tig, 2*tig+1, 2*tig+8, 2*tig+9  <->  tokens 16*ks + tig + {0, 8, 4, 12}
+      const uint32_t ones = 0x3c003c00u;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint2 pp = *reinterpret_cast<const uint2 *>(sm.pbuf[warp] + gid * PB_ROW + ks * 8 + 2 * tig);
+        const int t = 16 * ks + tig;
+        const uint32_t m0 = vm[t], m1 = vm[t + 8], m2 = vm[t + 4], m3 = vm[t + 12];       // (scale | zero << 16)
+        const uint32_t b0 = hmul2_u(pp.x, __byte_perm(m0, m1, 0x5410));
+        const uint32_t b1 = hmul2_u(pp.y, __byte_perm(m2, m3, 0x5410));
+        mma16816(cz, __byte_perm(m0, m1, 0x7632), ones, __byte_perm(m2, m3, 0x7632), ones, pp.x, pp.y);
+        const uint32_t w0 = vw[t * 8 + gid], w1 = vw[(t + 8) * 8 + gid], w2 = vw[(t + 4) * 8 + gid],
+                       w3 = vw[(t + 12) * 8 + gid];
+        const uint32_t xab = __byte_perm(w0, w1, 0x5410), yab = __byte_perm(w0, w1, 0x7632);
+        const uint32_t xcd = __byte_perm(w2, w3, 0x5410), ycd = __byte_perm(w2, w3, 0x7632);
+        const uint32_t xabs = xab >> 10, yabs = yab >> 10, xcds = xcd >> 10, ycds = ycd >> 10;
+#pragma unroll
+        for (int m = 0; m < 8; ++m)
+          mma16816(acc[m], field(xab, xabs, m), field(yab, yabs, m), field(xcd, xcds, m), field(ycd, ycds, m), b0, b1);
+      }
+      __syncwarp();      // every lane is done with this stage and with the probability buffer
+      ++seq;
+      const int nxt = pg + PG_STAGES * PG_WARPS;
+      if (nxt < p1) {
+        if (lane == 0) {
+          const uint32_t dst = smem_u32(&sm.stage[warp][st][0]);
+          const PairSrc src = pair_src(a, b, h, nxt);
+          mbar_expect_tx(bar, STAGE_BYTES);
+          bulk_g2s(dst + OFF_KREC, src.krec, K_HEAD, bar);
+          bulk_g2s(dst + OFF_KMETA, src.kmeta, META_HEAD, bar);
+          bulk_g2s(dst + OFF_VREC, src.vrec, V_HEAD, bar);
+          bulk_g2s(dst + OFF_VMETA, src.vmeta, META_HEAD, bar);
+        }
+        inflight |= 1u << st;
+      }
+    }
+
+    if (dead) {
+      // give copies still in flight a bounded time to land before the stages are reused or the block exits
+      for (int s = 0; s < PG_STAGES; ++s)
+        if (inflight & (1u << s)) {
+          mbar_wait(smem_u32(&sm.bar[warp][s]), ((seq + ((s + PG_STAGES - seq % PG_STAGES) % PG_STAGES)) / PG_STAGES) & 1u);
+          inflight &= ~(1u << s);
+        }
+    }
+    __syncthreads();     // all warps have consumed every copy they issued: the stages can be overlaid
+
+    // ---- warp result -> merge buffer [warp][head][PART] ---- //
+    float *mb = reinterpret_cast<float *>(&sm.stage[0][0][0]);
+    {
+      float *w = mb + warp * 8 * PART;
+#pragma unroll
+      for (int m = 0; m < 8; ++m) {
+        const float u = field_unscale(m);
+        w[(2 * tig) * PART + 16 * gid + m] = fmaf(acc[m][0], u, cz[0]);
+        w[(2 * tig + 1) * PART + 16 * gid + m] = fmaf(acc[m][1], u, cz[1]);
+        w[(2 * tig) * PART + 16 * gid + 8 + m] = fmaf(acc[m][2], u, cz[0]);
+        w[(2 * tig + 1) * PART + 16 * gid + 8 + m] = fmaf(acc[m][3], u, cz[1]);
+      }
+      if (gid == 0) {
+        w[(2 * tig) * PART + HD] = m_run0;
+        w[(2 * tig) * PART + HD + 1] = cz[2];
+        w[(2 * tig + 1) * PART + HD] = m_run1;
+        w[(2 * tig + 1) * PART + HD + 1] = cz[3];
+      }
+    }
+    __syncthreads();
+    {
+      float *dst = a.partials + ((static_cast<int64_t>(bh) * P.n_slots + (P.has_sink + c)) * G + gt * 8) * PART;
+      for (int g = 0; g < g_valid; ++g) {
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < PG_WARPS; ++w) M = fmaxf(M, mb[(w * 8 + g) * PART + HD]);
+        float A = 0.f, Ls = 0.f;
+#pragma unroll
+        for (int w = 0; w < PG_WARPS; ++w) {
+          const float mw = mb[(w * 8 + g) * PART + HD];
+          const float wt = (mw == -INFINITY) ? 0.f : ex2(mw - M);
+          A = fmaf(mb[(w * 8 + g) * PART + tid], wt, A);
+          Ls = fmaf(mb[(w * 8 + g) * PART + HD + 1], wt, Ls);
+        }
+        dst[g * PART + tid] = A;
+        if (tid == 0) {
+          dst[g * PART + HD] = M;
+          dst[g * PART + HD + 1] = Ls;
+        }
+      }
+    }
+  }
+}
+
+int launch_decode_paged(const DecodeArgs &a, int n_items, int n_gt, int grid, cudaStream_t s) {
+  static int configured = -1;     // per-process opt-in to > 48 KB dynamic shared memory, done once per device
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return KITTY_E_CUDA;
+  if (configured != dev) {
+    if (cudaFuncSetAttribute(decode_paged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(sizeof(PagedSmem))) != cudaSuccess)
+      return KITTY_E_CUDA;
+    configured = dev;
+  }
+  decode_paged_kernel<<<grid, PG_WARPS * 32, sizeof(PagedSmem), s>>>(a, n_items, n_gt);
+  return cudaGetLastError() == cudaSuccess ? KITTY_OK : KITTY_E_CUDA;
+}
+
+int paged_smem_bytes() { return static_cast<int>(sizeof(PagedSmem)); }
+
+}  // namespace kitty

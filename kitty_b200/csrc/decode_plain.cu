@@ -1,0 +1,230 @@
+// Plain (CUDA-core) decode-attention kernel and the slot merge kernel.
+//
+// The plain kernel reduces any run of tiles — sink, packed pages, Q-buffers,
+// the rotated value ring — with one thread per token (logits) and one thread
+// per channel (output).  It always handles the sink tile and the tail of a
+// sequence, where full-precision rows dominate and the byte count is small
+// (a few hundred tokens per (batch, kv-head)); with impl=1 it handles the packed
+// pages too and serves as an in-library cross-check of the streaming kernel.
+//
+// Dequantisation is `code * scale + min` evaluated in fp32 from the fp16
+// metadata (kernels/kitty_attention.py:162-165, 317-320 of the reference do it in
+// fp16; the difference is inside the stated attention tolerance).
+#include "decode.cuh"
+
+namespace kitty {
+
+struct PlainSmem {
+  float q[MAX_GROUP][HD];          // query * scaling * log2(e)
+  float sl[PAGE][MAX_GROUP + 1];   // logits, then probabilities
+  __align__(16) uint8_t krec[K_HEAD];
+  __align__(16) __half2 kmeta[HD];
+  __align__(16) uint8_t vrec[V_HEAD];
+  __align__(16) __half2 vmeta[PAGE];
+  float m_run[MAX_GROUP], l_run[MAX_GROUP], alpha[MAX_GROUP];
+};
+
+__global__ void __launch_bounds__(128) decode_plain_kernel(DecodeArgs a) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  PlainSmem &sm = *reinterpret_cast<PlainSmem *>(smem_raw);
+  const DecodePlan &P = a.P;
+  const kitty_counts &C = a.C;
+  const int tid = threadIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z, H = P.H, G = P.G;
+  const int64_t bh = static_cast<int64_t>(b) * H + h;
+
+  // ---- which tiles, which slot ---- //
+  int u0, u1, slot;
+  {
+    int j = blockIdx.x;
+    if (P.has_sink && j == 0) {
+      u0 = 0; u1 = 1; slot = 0;
+    } else {
+      j -= P.has_sink;
+      if (!P.fast_chunks && j < P.nchunk) {
+        const int p0 = P.pb + j * P.ch;
+        const int p1 = min(P.pe, p0 + P.ch);
+        u0 = 1 + p0; u1 = 1 + p1; slot = P.has_sink + j;
+      } else {
+        u0 = C.PageCount_V + 1; u1 = P.n_tiles; slot = P.has_sink + P.nchunk;
+      }
+    }
+  }
+  const int t_pos = C.PageCount_K * PAGE + C.Q_Buffer_Count_K;   // tokens after the sink
+
+  for (int i = tid; i < G * HD; i += 128) {
+    const int g = i / HD, d = i % HD;
+    sm.q[g][d] = load_q(a.q, a.q_dtype, (static_cast<int64_t>(b) * P.h_q + h * G + g) * HD + d) * a.scale_log2;
+  }
+  if (tid < MAX_GROUP) {
+    sm.m_run[tid] = -INFINITY;
+    sm.l_run[tid] = 0.f;
+  }
+  float out[MAX_GROUP];
+#pragma unroll
+  for (int g = 0; g < MAX_GROUP; ++g) out[g] = 0.f;
+  __syncthreads();
+
+  for (int u = u0; u < u1; ++u) {
+    const int n = (u == 0) ? C.Sink_Count : min(PAGE, t_pos - (u - 1) * PAGE);
+    if (n <= 0) continue;
+    const bool k_packed = (u >= 1) && (u - 1 < C.PageCount_K);
+    const bool v_packed = (u >= 1) && (u - 1 < C.PageCount_V);
+    if (k_packed) {
+      const int64_t pid = a.L.PageTable_K[static_cast<int64_t>(b) * a.L.max_page + (u - 1)];
+      const uint4 *src = reinterpret_cast<const uint4 *>(a.L.KeyCache + pid * (static_cast<int64_t>(H) * K_HEAD) + h * K_HEAD);
+      for (int i = tid; i < K_HEAD / 16; i += 128) reinterpret_cast<uint4 *>(sm.krec)[i] = src[i];
+      const uint4 *ms = reinterpret_cast<const uint4 *>(static_cast<const __half2 *>(a.L.KeyCache_metadata) + (pid * H + h) * HD);
+      if (tid < META_HEAD / 16) reinterpret_cast<uint4 *>(sm.kmeta)[tid] = ms[tid];
+    }
+    if (v_packed) {
+      const int64_t pid = a.L.PageTable_V[static_cast<int64_t>(b) * a.L.max_page + (u - 1)];
+      const uint4 *src = reinterpret_cast<const uint4 *>(a.L.ValueCache + pid * (static_cast<int64_t>(H) * V_HEAD) + h * V_HEAD);
+      for (int i = tid; i < V_HEAD / 16; i += 128) reinterpret_cast<uint4 *>(sm.vrec)[i] = src[i];
+      const uint4 *ms = reinterpret_cast<const uint4 *>(static_cast<const __half2 *>(a.L.ValueCache_metadata) + (pid * H + h) * PAGE);
+      if (tid < META_HEAD / 16) reinterpret_cast<uint4 *>(sm.vmeta)[tid] = ms[tid];
+    }
+    __syncthreads();
+
+    // ---- logits: thread = token ---- //
+    if (tid < n) {
+      float acc[MAX_GROUP];
+#pragma unroll
+      for (int g = 0; g < MAX_GROUP; ++g) acc[g] = 0.f;
+      if (k_packed) {
+        const int col = tid >> 2, sh = (tid & 3) * 2;
+        for (int d = 0; d < HD; ++d) {
+          uint32_t code = (sm.krec[d * K_ROW + col] >> sh) & 3u;
+          const uint32_t s = sm.krec[K_OFF_IDX + d];
+          if (s < DB) code |= ((sm.krec[K_OFF_HI + s * K_ROW + col] >> sh) & 3u) << 2;
+          const float2 mt = __half22float2(sm.kmeta[d]);
+          const float kv = static_cast<float>(code) * mt.x + mt.y;
+#pragma unroll
+          for (int g = 0; g < MAX_GROUP; ++g)
+            if (g < G) acc[g] = fmaf(sm.q[g][d], kv, acc[g]);
+        }
+      } else {
+        const __half *row;
+        if (u == 0) row = static_cast<const __half *>(a.L.Sink_Buffer_K) + (bh * SINK + tid) * HD;
+        else row = static_cast<const __half *>(a.L.Q_Buffer_K) + (bh * PAGE + ((u - 1 - C.PageCount_K) * PAGE + tid)) * HD;
+        for (int d8 = 0; d8 < HD / 8; ++d8) {
+          float kv[8];
+          Vec8<__half>::load(row + 8 * d8, kv);
+#pragma unroll
+          for (int g = 0; g < MAX_GROUP; ++g)
+            if (g < G) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) acc[g] = fmaf(sm.q[g][8 * d8 + e], kv[e], acc[g]);
+            }
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < MAX_GROUP; ++g)
+        if (g < G) sm.sl[tid][g] = acc[g];
+    }
+    __syncthreads();
+    // ---- running max ---- //
+    if (tid < G) {
+      float mx = -INFINITY;
+      for (int t = 0; t < n; ++t) mx = fmaxf(mx, sm.sl[t][tid]);
+      const float mo = sm.m_run[tid], mn = fmaxf(mo, mx);
+      sm.alpha[tid] = (mo == -INFINITY) ? 0.f : exp2f(mo - mn);
+      sm.m_run[tid] = mn;
+    }
+    __syncthreads();
+    if (tid < n) {
+#pragma unroll
+      for (int g = 0; g < MAX_GROUP; ++g)
+        if (g < G) sm.sl[tid][g] = exp2f(sm.sl[tid][g] - sm.m_run[g]);
+    }
+    __syncthreads();
+    if (tid < G) {
+      float s = 0.f;
+      for (int t = 0; t < n; ++t) s += sm.sl[t][tid];
+      sm.l_run[tid] = sm.l_run[tid] * sm.alpha[tid] + s;
+    }
+    // ---- output: thread = channel ---- //
+#pragma unroll
+    for (int g = 0; g < MAX_GROUP; ++g)
+      if (g < G) out[g] *= sm.alpha[g];
+    if (v_packed) {
+      const int col = tid >> 2, sh = (tid & 3) * 2;
+      for (int t = 0; t < n; ++t) {
+        const uint32_t code = (sm.vrec[t * V_ROW + col] >> sh) & 3u;
+        const float2 mt = __half22float2(sm.vmeta[t]);
+        const float v = static_cast<float>(code) * mt.x + mt.y;
+#pragma unroll
+        for (int g = 0; g < MAX_GROUP; ++g)
+          if (g < G) out[g] = fmaf(sm.sl[t][g], v, out[g]);
+      }
+    } else {
+      for (int t = 0; t < n; ++t) {
+        const __half *row;
+        if (u == 0) {
+          row = static_cast<const __half *>(a.L.Sink_Buffer_V) + (bh * SINK + t) * HD;
+        } else {
+          const int r = (u - 1 - C.PageCount_V) * PAGE + t;       // position after the packed value pages
+          if (r < C.Q_Buffer_Count_V) row = static_cast<const __half *>(a.L.Q_Buffer_V) + (bh * PAGE + r) * HD;
+          else row = static_cast<const __half *>(a.L.Local_Buffer_V) + (bh * PAGE + ((r - C.Q_Buffer_Count_V + C.Write_Offset_Local_V) & (PAGE - 1))) * HD;
+        }
+        const float v = __half2float(row[tid]);
+#pragma unroll
+        for (int g = 0; g < MAX_GROUP; ++g)
+          if (g < G) out[g] = fmaf(sm.sl[t][g], v, out[g]);
+      }
+    }
+    __syncthreads();
+  }
+
+  float *dst = a.partials + ((bh * P.n_slots + slot) * G) * PART;
+#pragma unroll
+  for (int g = 0; g < MAX_GROUP; ++g)
+    if (g < G) dst[g * PART + tid] = out[g];
+  if (tid < G) {
+    dst[tid * PART + HD] = sm.m_run[tid];
+    dst[tid * PART + HD + 1] = sm.l_run[tid];
+  }
+}
+
+__global__ void __launch_bounds__(128) merge_kernel(MergeArgs a) {
+  const int64_t r = blockIdx.x;
+  const int c = threadIdx.x;
+  const float *base = a.partials + ((r / a.gm) * a.ns * a.gm + r % a.gm) * PART;
+  float M = -INFINITY;
+  for (int s = 0; s < a.n; ++s) M = fmaxf(M, base[s * a.stride_part + HD]);
+  float A = 0.f, Lsum = 0.f;
+  for (int s = 0; s < a.n; ++s) {
+    const float *p = base + s * a.stride_part;
+    const float ms = p[HD];
+    const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
+    A = fmaf(p[c], w, A);
+    Lsum = fmaf(p[HD + 1], w, Lsum);
+  }
+  if (a.partial_out) {
+    float *o = a.partial_out + r * PART;
+    o[c] = A;
+    if (c == 0) {
+      o[HD] = M;
+      o[HD + 1] = Lsum;
+    }
+    return;
+  }
+  const float v = A / Lsum;
+  if (a.out_dtype == KITTY_F16) static_cast<__half *>(a.out)[r * HD + c] = __float2half_rn(v);
+  else if (a.out_dtype == KITTY_BF16) static_cast<__nv_bfloat16 *>(a.out)[r * HD + c] = __float2bfloat16_rn(v);
+  else static_cast<float *>(a.out)[r * HD + c] = v;
+}
+
+int launch_decode_plain(const DecodeArgs &a, int items_per_bh, cudaStream_t s) {
+  dim3 grid(items_per_bh, a.P.H, a.P.B);
+  decode_plain_kernel<<<grid, 128, sizeof(PlainSmem), s>>>(a);
+  return cudaGetLastError() == cudaSuccess ? KITTY_OK : KITTY_E_CUDA;
+}
+
+int launch_merge(const MergeArgs &m, cudaStream_t s) {
+  if (m.rows == 0) return KITTY_OK;
+  merge_kernel<<<static_cast<unsigned>(m.rows), 128, 0, s>>>(m);
+  return cudaGetLastError() == cudaSuccess ? KITTY_OK : KITTY_E_CUDA;
+}
+
+}  // namespace kitty

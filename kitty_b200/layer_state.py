@@ -1,0 +1,103 @@
+"""Per-layer device buffers of the Kitty cache.
+
+Field names, shapes, dtypes and the byte layout of the packed pages are those of
+the reference's `KVCache_Layer` (src/kitty/kvcache/utils_kv_per_layer.py:18-95),
+so code written against that object keeps working.  Differences: the device is a
+constructor argument instead of the literal 'cuda', the identity page tables are
+filled with one `arange` instead of a Python loop of single-element writes, and
+the object carries the C structs the kernels take.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+PAGE_SIZE = 128
+SINK = 32
+
+
+class KVCache_Layer:
+    def __init__(self, MAX_BS: int, MAX_LEN: int, H_KV: int, D: int, D_BOOSTED: int, LOW_BIT: int, HIGH_BIT: int,
+                 PAGE_SIZE: int, S: int, device="cuda"):
+        if (PAGE_SIZE, D, D_BOOSTED, S, LOW_BIT, HIGH_BIT) != (128, 128, 32, 32, 2, 4):
+            raise ValueError("kitty_b200 kernels are built for PAGE_SIZE=128, D=128, D_BOOSTED=32, S=32, 2/4 bit; got "
+                             f"{(PAGE_SIZE, D, D_BOOSTED, S, LOW_BIT, HIGH_BIT)}")
+        dev = torch.device(device)
+        if dev.type != "cuda":
+            raise ValueError("kitty_b200 buffers live on a CUDA device (there is no CPU path)")
+        self.BITS_PER_BYTE = 8
+        self.HIGH_BIT, self.LOW_BIT = HIGH_BIT, LOW_BIT
+        self.MAX_BS, self.MAX_LEN, self.H_KV, self.D = MAX_BS, MAX_LEN, H_KV, D
+        self.D_BOOSTED, self.PAGE_SIZE, self.S = D_BOOSTED, PAGE_SIZE, S
+        self.device = dev
+        self.MAX_PAGE = math.ceil(MAX_LEN / PAGE_SIZE)
+        row = PAGE_SIZE * LOW_BIT // 8                       # bytes of one channel row (keys) / token row (values)
+        self.bytes_per_page_K = H_KV * (row * (D + D_BOOSTED) + D)
+        self.bytes_per_page_V = H_KV * row * PAGE_SIZE
+        n = MAX_BS * self.MAX_PAGE
+        z = dict(device=dev)
+        self.KeyCache = torch.zeros((n, self.bytes_per_page_K), dtype=torch.uint8, **z)
+        self.KeyCache_metadata = torch.zeros((n, H_KV, D, 2), dtype=torch.float16, **z)
+        self.ValueCache = torch.zeros((n, self.bytes_per_page_V), dtype=torch.uint8, **z)
+        self.ValueCache_metadata = torch.zeros((n, H_KV, PAGE_SIZE, 2), dtype=torch.float16, **z)
+        self.PageTable_K = torch.arange(n, dtype=torch.int64, **z).view(MAX_BS, self.MAX_PAGE).contiguous()
+        self.PageTable_V = self.PageTable_K.clone()
+        self.PageCount_K = 0
+        self.PageCount_V = 0
+        self.Sink_Buffer_K = torch.zeros((MAX_BS, H_KV, S, D), dtype=torch.float16, **z)
+        self.Sink_Buffer_V = torch.zeros((MAX_BS, H_KV, S, D), dtype=torch.float16, **z)
+        self.Sink_Count = 0
+        self.Q_Buffer_K = torch.zeros((MAX_BS, H_KV, PAGE_SIZE, D), dtype=torch.float16, **z)
+        self.Q_Buffer_V = torch.zeros((MAX_BS, H_KV, PAGE_SIZE, D), dtype=torch.float16, **z)
+        self.Q_Buffer_Count_K = 0
+        self.Q_Buffer_Count_V = 0
+        self.Local_Buffer_V = torch.zeros((MAX_BS, H_KV, PAGE_SIZE, D), dtype=torch.float16, **z)
+        self.Local_Count_V = 0
+        self.Write_Offset_Local_V = 0
+        self.key_states: Optional[torch.Tensor] = None
+        self.value_states: Optional[torch.Tensor] = None
+        self._c_layer = None
+        self._workspace: Optional[torch.Tensor] = None
+
+    # -- reference surface ------------------------------------------------- #
+    def get_total_length(self) -> int:
+        seqlen_k = self.PageCount_K * self.PAGE_SIZE + self.Sink_Count + self.Q_Buffer_Count_K
+        seqlen_v = self.PageCount_V * self.PAGE_SIZE + self.Sink_Count + self.Q_Buffer_Count_V + self.Local_Count_V
+        assert seqlen_k == seqlen_v, f"seqlen_K: {seqlen_k}, seqlen_V: {seqlen_v}"
+        return seqlen_k
+
+    # -- C-ABI views --------------------------------------------------------- #
+    def c_layer(self) -> "_lib.KittyLayer":
+        """struct kitty_layer pointing at this layer's tensors (built once; the tensors are never reallocated)."""
+        if self._c_layer is None:
+            L = _lib.KittyLayer()
+            L.max_bs, L.max_page, L.h_kv, L.head_dim = self.MAX_BS, self.MAX_PAGE, self.H_KV, self.D
+            L.d_boost, L.page_size, L.sink_size, L.reserved = self.D_BOOSTED, self.PAGE_SIZE, self.S, 0
+            for name in ("KeyCache", "KeyCache_metadata", "ValueCache", "ValueCache_metadata", "PageTable_K",
+                         "PageTable_V", "Sink_Buffer_K", "Sink_Buffer_V", "Q_Buffer_K", "Q_Buffer_V",
+                         "Local_Buffer_V"):
+                t = getattr(self, name)
+                assert t.is_contiguous()
+                setattr(L, name, t.data_ptr())
+            self._c_layer = L
+        return self._c_layer
+
+    def c_counts(self) -> "_lib.KittyCounts":
+        c = _lib.KittyCounts()
+        c.PageCount_K, c.PageCount_V, c.Sink_Count = self.PageCount_K, self.PageCount_V, self.Sink_Count
+        c.Q_Buffer_Count_K, c.Q_Buffer_Count_V = self.Q_Buffer_Count_K, self.Q_Buffer_Count_V
+        c.Local_Count_V, c.Write_Offset_Local_V, c.reserved = self.Local_Count_V, self.Write_Offset_Local_V, 0
+        return c
+
+    def workspace(self, batch: int, h_q: int) -> torch.Tensor:
+        """Zero-initialised scratch for the decode kernels, allocated on first use and kept."""
+        need = _lib.lib().kitty_decode_workspace_bytes(batch, self.H_KV, h_q, self.MAX_PAGE)
+        if need < 0:
+            _lib.check(int(need), "kitty_decode_workspace_bytes")
+        if self._workspace is None or self._workspace.numel() < need:
+            self._workspace = torch.zeros(int(need), dtype=torch.uint8, device=self.device)
+        return self._workspace
