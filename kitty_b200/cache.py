@@ -41,7 +41,7 @@ class KittyCache(Cache):
         self.high_bit = 4
         self.selection = selection
         self.div_mode = div_mode
-        self.max_batch_size, self.max_length = max_batch_size, max_length
+        self._kitty_max_batch, self._kitty_max_length = max_batch_size, max_length
         self.kv_cache: list[KVCache_Layer] = [
             KVCache_Layer(MAX_BS=max_batch_size, MAX_LEN=max_length, H_KV=self.num_key_value_heads, D=self.head_dim,
                           D_BOOSTED=self.d_boosted, LOW_BIT=self.low_bit, HIGH_BIT=self.high_bit,
@@ -161,7 +161,7 @@ class KittyCache(Cache):
         return self.get_seq_length(layer_idx) + query_length, 0
 
     def get_max_cache_shape(self, layer_idx: int = 0) -> int:
-        return self.max_length
+        return self._kitty_max_length
 
     def __len__(self) -> int:
         return self.num_hidden_layers

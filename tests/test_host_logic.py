@@ -1,0 +1,112 @@
+"""Host-side state machine of KittyCache, run on CPU against a recording stand-in
+for the CUDA library: the counters must follow the oracle's (i.e. the
+reference's) transitions and the right entry points must be called."""
+import types
+
+import pytest
+import torch
+
+from oracle import kitty_oracle as ko
+from tests.helpers import COUNTERS
+
+
+class FakeLayer:
+    """Counters and geometry only; no device buffers."""
+
+    def __init__(self, MAX_BS, MAX_LEN, H_KV, D, D_BOOSTED, LOW_BIT, HIGH_BIT, PAGE_SIZE, S, device="cuda"):
+        self.MAX_BS, self.MAX_LEN, self.H_KV, self.D, self.D_BOOSTED = MAX_BS, MAX_LEN, H_KV, D, D_BOOSTED
+        self.PAGE_SIZE, self.S, self.device = PAGE_SIZE, S, torch.device("cpu")
+        self.MAX_PAGE = -(-MAX_LEN // PAGE_SIZE)
+        for c in COUNTERS:
+            setattr(self, c, 0)
+        self.key_states = self.value_states = None
+        for n in ("PageTable_K", "PageTable_V", "KeyCache", "KeyCache_metadata", "ValueCache", "ValueCache_metadata",
+                  "Q_Buffer_K", "Q_Buffer_V"):
+            setattr(self, n, None)
+
+    def c_layer(self):
+        return None
+
+    def c_counts(self):
+        return tuple(getattr(self, c) for c in COUNTERS)
+
+    def get_total_length(self):
+        k = self.PageCount_K * 128 + self.Sink_Count + self.Q_Buffer_Count_K
+        v = self.PageCount_V * 128 + self.Sink_Count + self.Q_Buffer_Count_V + self.Local_Count_V
+        assert k == v
+        return k
+
+
+@pytest.fixture
+def fake(monkeypatch):
+    import kitty_b200.cache as cache_mod
+    from kitty_b200 import _lib
+
+    calls = []
+
+    class Rec:
+        def __getattr__(self, name):
+            def f(*a):
+                calls.append((name, a))
+                return 0
+            return f
+
+    monkeypatch.setattr(cache_mod, "KVCache_Layer", FakeLayer)
+    monkeypatch.setattr(_lib, "lib", lambda: Rec())
+    monkeypatch.setattr(_lib, "stream_ptr", lambda d: 0)
+    monkeypatch.setattr(cache_mod, "quantize_pack_k", lambda *a, **k: calls.append(("pack_k", a)))
+    monkeypatch.setattr(cache_mod, "quantize_pack_v", lambda *a, **k: calls.append(("pack_v", a)))
+    return cache_mod, calls
+
+
+@pytest.mark.parametrize("L", [1, 20, 32, 33, 159, 160, 161, 288, 289, 32 + 3 * 128 + 57])
+def test_counters_follow_the_reference_state_machine(fake, L):
+    cache_mod, calls = fake
+    cfg = types.SimpleNamespace(num_hidden_layers=2, head_dim=128, num_key_value_heads=2, num_attention_heads=8,
+                                hidden_size=1024)
+    steps = 300
+    cache = cache_mod.KittyCache(cfg, 1, L + steps + 8)
+    oc = ko.OracleKittyCache(2, 2, 128, 1, L + steps + 8, select=lambda pages, dt: torch.zeros(pages.shape[:-2] + (128,), dtype=torch.uint8).numpy())
+    k = torch.zeros(1, 2, L, 128, dtype=torch.float16)
+    for layer in (0, 1):
+        assert cache.update(k, k, layer) is True and oc.update(k, k, layer) is True
+        cache.quantize_prefill(layer)
+        oc.quantize_prefill(layer)
+        assert cache.kv_cache[layer].key_states is None
+    tok = torch.zeros(1, 2, 1, 128, dtype=torch.float16)
+    for s in range(steps):
+        for layer in (0, 1):
+            assert cache.update(tok, tok, layer) is False
+            oc.update(tok, tok, layer)
+            cache.quantize_decode(layer)
+            oc.quantize_decode(layer)
+            got = [getattr(cache.kv_cache[layer], c) for c in COUNTERS]
+            want = [getattr(oc.kv_cache[layer], c) for c in COUNTERS]
+            assert got == want, (s, layer, got, want)
+        assert cache.get_seq_length(0) == L + s + 1
+    names = [c[0] for c in calls]
+    assert names.count("kitty_prefill_tails") == 2
+    assert names.count("kitty_append") == 2 * steps
+    p = ko.prefill_partition(L)
+    assert names.count("pack_k") == (2 if p["pages_k"] else 0)
+    flushes = [c for c in calls if c[0] == "kitty_flush"]
+    final = oc.kv_cache[0]
+    k_flushed = sum(1 for c in flushes if c[1][3]) // 2
+    v_flushed = sum(1 for c in flushes if c[1][4]) // 2
+    assert k_flushed == final.PageCount_K - p["pages_k"] and v_flushed == final.PageCount_V - p["pages_v"]
+
+
+def test_update_rejects_multi_token_decode(fake):
+    cache_mod, _ = fake
+    cfg = types.SimpleNamespace(num_hidden_layers=1, head_dim=128, num_key_value_heads=1, num_attention_heads=4,
+                                hidden_size=512)
+    cache = cache_mod.KittyCache(cfg, 1, 512)
+    k = torch.zeros(1, 1, 40, 128, dtype=torch.float16)
+    cache.update(k, k, 0)
+    cache.quantize_prefill(0)
+    with pytest.raises(AssertionError):
+        cache.update(k, k, 0)
+    with pytest.raises(ValueError):
+        cache.quantize_prefill(0)
+    assert cache.get_mask_sizes(torch.arange(1), 0) == (41, 0)
+    assert len(cache) == 1 and cache.get_max_cache_shape() == 512
