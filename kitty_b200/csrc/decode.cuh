@@ -28,6 +28,8 @@ struct DecodePlan {
   int32_t n_slots;       // has_sink + nchunk + has_tail
   int32_t n_tiles;       // total tiles of the sequence (sink tile included)
   int32_t fast_chunks;   // 1: chunks are reduced by the streaming kernel, 0: by the plain kernel
+  int32_t chunk_slot0;   // slot of chunk 0
+  int32_t edge_slot;     // slot written by the edge kernel (sink + tail together), when it runs
 };
 
 struct DecodeArgs {
@@ -54,6 +56,7 @@ struct MergeArgs {
 
 int launch_decode_plain(const DecodeArgs &a, int items_per_bh, cudaStream_t s);
 int launch_decode_paged(const DecodeArgs &a, int n_items, int n_gt, int grid, cudaStream_t s);
+int launch_decode_edge(const DecodeArgs &a, cudaStream_t s);
 int launch_merge(const MergeArgs &m, cudaStream_t s);
 
 __device__ __forceinline__ float load_q(const void *q, int dtype, int64_t i) {

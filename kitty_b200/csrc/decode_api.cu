@@ -111,8 +111,17 @@ extern "C" int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *c
   const int n_gt = (G + 7) / 8;
   const int grid_max = 2 * sm_count();
   plan_chunks(P.pe - P.pb, static_cast<int64_t>(B) * H * n_gt, grid_max, &P.ch, &P.nchunk);
-  P.n_slots = P.has_sink + P.nchunk + P.has_tail;
   P.fast_chunks = (impl == 0) ? 1 : 0;
+  const int has_edge = (P.has_sink || P.has_tail) ? 1 : 0;
+  if (P.fast_chunks) {            // slots: [edge?][chunks]
+    P.n_slots = has_edge + P.nchunk;
+    P.chunk_slot0 = has_edge;
+    P.edge_slot = 0;
+  } else {                        // slots: [sink?][chunks][tail?]
+    P.n_slots = P.has_sink + P.nchunk + P.has_tail;
+    P.chunk_slot0 = P.has_sink;
+    P.edge_slot = 0;
+  }
   if (P.n_slots == 0 && !partial_out) return KITTY_E_BADARG;                      // nothing to attend to
 
   const int64_t need = WS_HEADER + static_cast<int64_t>(B) * H * P.n_slots * G * PART * static_cast<int64_t>(sizeof(float));
@@ -129,9 +138,14 @@ extern "C" int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *c
     const int grid = static_cast<int>(std::min<int64_t>(items, grid_max));
     if (int rc = launch_decode_paged(a, static_cast<int>(items), n_gt, grid, s)) return rc;
   }
-  const int plain_items = P.has_sink + (P.fast_chunks ? 0 : P.nchunk) + P.has_tail;
-  if (plain_items > 0)
-    if (int rc = launch_decode_plain(a, plain_items, s)) return rc;
+  if (P.fast_chunks) {
+    if (has_edge)
+      if (int rc = launch_decode_edge(a, s)) return rc;
+  } else {
+    const int plain_items = P.has_sink + P.nchunk + P.has_tail;
+    if (plain_items > 0)
+      if (int rc = launch_decode_plain(a, plain_items, s)) return rc;
+  }
 
   MergeArgs m;
   m.partials = a.partials;

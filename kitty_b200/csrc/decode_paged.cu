@@ -21,7 +21,7 @@
 // chain also yielding the softmax denominator from a row of ones.
 //
 // Per (page pair, warp): 160 mma.sync, ~1.2 k other instructions.
-#include "decode.cuh"
+#include "paged_core.cuh"
 
 namespace kitty {
 
@@ -34,8 +34,6 @@ constexpr int OFF_VMETA = OFF_VREC + V_HEAD;        // 9856
 constexpr int STAGE_BYTES = OFF_VMETA + META_HEAD;  // 10368
 constexpr int PB_ROW = 68;                          // words per query-head row of the probability buffer (64 + pad)
 constexpr int PB_WORDS = 8 * PB_ROW;
-constexpr int QS_ROW = HD + 8;                      // halves per row of the staged query
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
 struct PagedSmem {
   __align__(128) uint8_t stage[PG_WARPS][PG_STAGES][STAGE_BYTES];
@@ -45,67 +43,6 @@ struct PagedSmem {
   uint8_t inv[PG_WARPS][DB];
 };
 static_assert(PG_WARPS * 8 * PART * 4 <= PG_WARPS * PG_STAGES * STAGE_BYTES, "merge buffer overlays the stages");
-
-// ---- PTX wrappers --------------------------------------------------------- //
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait: false when the copy did not land within the limit.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  return false;
-}
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ float ex2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ uint32_t hmul2_u(uint32_t a, uint32_t b) {
-  __half2 r = __hmul2(*reinterpret_cast<__half2 *>(&a), *reinterpret_cast<__half2 *>(&b));
-  return *reinterpret_cast<uint32_t *>(&r);
-}
-__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
-  __half2 r = __floats2half2_rn(lo, hi);
-  return *reinterpret_cast<uint32_t *>(&r);
-}
-
-// Field f (0..7) of both 16-bit halves of x as an fp16x2 operand, and the power
-// of two that undoes its weight.  Fields 5..7 sit in the exponent bits, so they
-// are taken from the copy shifted right by 10 (xs), where they are fields 0..2.
-__device__ __forceinline__ uint32_t field(uint32_t x, uint32_t xs, int f) {
-  return (f < 5) ? (x & (0x00030003u << (2 * f))) : (xs & (0x00030003u << (2 * (f - 5))));
-}
-__host__ __device__ constexpr float field_unscale(int f) {
-  // 2^24 / 4^pos, pos = f for f < 5 and f - 5 otherwise
-  return 16777216.0f / static_cast<float>(1 << (2 * (f < 5 ? f : f - 5)));
-}
 
 struct PairSrc {
   const uint8_t *krec, *kmeta, *vrec, *vmeta;
@@ -184,17 +121,8 @@ __global__ void __launch_bounds__(PG_WARPS * 32) decode_paged_kernel(DecodeArgs 
     inflight = __shfl_sync(0xffffffffu, inflight, 0);
     __syncthreads();   // staged query visible
 
-    // query fragments: B operand column n = gid (query head), contraction index
-    // k = 2*tig, 2*tig+1, 2*tig+8, 2*tig+9  <->  channels 16*ks + tig + {0, 4, 8, 12}
     uint32_t q2[8][2];
-#pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
-      const __half *qr = &sm.qs[gid][16 * ks + tig];
-      __half2 x = __halves2half2(qr[0], qr[4]);
-      __half2 y = __halves2half2(qr[8], qr[12]);
-      q2[ks][0] = *reinterpret_cast<uint32_t *>(&x);
-      q2[ks][1] = *reinterpret_cast<uint32_t *>(&y);
-    }
+    load_q_frags(sm.qs, gid, tig, q2);
 
     float acc[8][4];       // out[channel 16*gid + m (+8)][head 2*tig (+1)], still carrying the field weight
     float cz[4] = {0.f, 0.f, 0.f, 0.f};   // [0,1]: sum p*zero-point, [2,3]: sum p, heads 2*tig, 2*tig+1
@@ -213,78 +141,17 @@ __global__ void __launch_bounds__(PG_WARPS * 32) decode_paged_kernel(DecodeArgs 
       }
       inflight &= ~(1u << st);
       const uint8_t *stg = sm.stage[warp][st];
-      const uint32_t *kw = reinterpret_cast<const uint32_t *>(stg + OFF_KREC);
-      const uint32_t *hw = reinterpret_cast<const uint32_t *>(stg + OFF_KREC + K_OFF_HI);
-      const uint32_t *km = reinterpret_cast<const uint32_t *>(stg + OFF_KMETA);
       const uint32_t *vw = reinterpret_cast<const uint32_t *>(stg + OFF_VREC);
       const uint32_t *vm = reinterpret_cast<const uint32_t *>(stg + OFF_VMETA);
 
-      // slot -> channel table of this page
-      {
-        const uint32_t w = *reinterpret_cast<const uint32_t *>(stg + OFF_KREC + K_OFF_IDX + 4 * lane);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint32_t s = (w >> (8 * i)) & 0xffu;
-          if (s < DB) sm.inv[warp][s] = static_cast<uint8_t>(4 * lane + i);
-        }
-      }
-
       // ================= Q K^T ================= //
-      float cl[8][4];    // logits[token 16*gid + m (+8)][head 2*tig (+1)], carrying the field weight
-      float cb[4] = {0.f, 0.f, 0.f, 0.f};   // sum_d q*min, identical in every row
-#pragma unroll
-      for (int m = 0; m < 8; ++m) cl[m][0] = cl[m][1] = cl[m][2] = cl[m][3] = 0.f;
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const int ch = 16 * ks + tig;
-        const uint32_t m0 = km[ch], m1 = km[ch + 4], m2 = km[ch + 8], m3 = km[ch + 12];   // (scale | min << 16)
-        const uint32_t b0 = hmul2_u(q2[ks][0], __byte_perm(m0, m1, 0x5410));
-        const uint32_t b1 = hmul2_u(q2[ks][1], __byte_perm(m2, m3, 0x5410));
-        const uint32_t mnA = __byte_perm(m0, m1, 0x7632), mnB = __byte_perm(m2, m3, 0x7632);
-        mma16816(cb, mnA, mnA, mnB, mnB, q2[ks][0], q2[ks][1]);
-        const uint32_t w0 = kw[ch * 8 + gid], w1 = kw[(ch + 4) * 8 + gid], w2 = kw[(ch + 8) * 8 + gid],
-                       w3 = kw[(ch + 12) * 8 + gid];
-        const uint32_t xab = __byte_perm(w0, w1, 0x5410), yab = __byte_perm(w0, w1, 0x7632);
-        const uint32_t xcd = __byte_perm(w2, w3, 0x5410), ycd = __byte_perm(w2, w3, 0x7632);
-        const uint32_t xabs = xab >> 10, yabs = yab >> 10, xcds = xcd >> 10, ycds = ycd >> 10;
-#pragma unroll
-        for (int m = 0; m < 8; ++m)
-          mma16816(cl[m], field(xab, xabs, m), field(yab, yabs, m), field(xcd, xcds, m), field(ycd, ycds, m), b0, b1);
-      }
-      __syncwarp();      // slot table complete
-      // high plane: contraction over slots 16*hs + tig + {0,4,8,12}; operand = 4 * q * scale of the slot's channel
-#pragma unroll
-      for (int hs = 0; hs < 2; ++hs) {
-        const int sl = 16 * hs + tig;
-        uint32_t bq[2];
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const int ca = sm.inv[warp][sl + 8 * j], cb2 = sm.inv[warp][sl + 8 * j + 4];
-          const __half2 qq = __halves2half2(sm.qs[gid][ca], sm.qs[gid][cb2]);
-          const __half2 ss = __halves2half2(__ushort_as_half(static_cast<unsigned short>(km[ca] & 0xffffu)),
-                                            __ushort_as_half(static_cast<unsigned short>(km[cb2] & 0xffffu)));
-          const __half2 r = __hmul2(__hmul2(qq, ss), __float2half2_rn(4.0f));
-          bq[j] = *reinterpret_cast<const uint32_t *>(&r);
-        }
-        const uint32_t w0 = hw[sl * 8 + gid], w1 = hw[(sl + 4) * 8 + gid], w2 = hw[(sl + 8) * 8 + gid],
-                       w3 = hw[(sl + 12) * 8 + gid];
-        const uint32_t xab = __byte_perm(w0, w1, 0x5410), yab = __byte_perm(w0, w1, 0x7632);
-        const uint32_t xcd = __byte_perm(w2, w3, 0x5410), ycd = __byte_perm(w2, w3, 0x7632);
-        const uint32_t xabs = xab >> 10, yabs = yab >> 10, xcds = xcd >> 10, ycds = ycd >> 10;
-#pragma unroll
-        for (int m = 0; m < 8; ++m)
-          mma16816(cl[m], field(xab, xabs, m), field(yab, yabs, m), field(xcd, xcds, m), field(ycd, ycds, m), bq[0], bq[1]);
-      }
+      float cl[8][4];    // logits[token 16*gid + m (+8)][head 2*tig (+1)]
+      qk_packed_page(stg + OFF_KREC, reinterpret_cast<const uint32_t *>(stg + OFF_KMETA), sm.qs, q2, sm.inv[warp], lane, cl);
 
       // ================= online softmax ================= //
       float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
       for (int m = 0; m < 8; ++m) {
-        const float u = field_unscale(m);
-        cl[m][0] = fmaf(cl[m][0], u, cb[0]);
-        cl[m][1] = fmaf(cl[m][1], u, cb[1]);
-        cl[m][2] = fmaf(cl[m][2], u, cb[2]);
-        cl[m][3] = fmaf(cl[m][3], u, cb[3]);
         mx0 = fmaxf(mx0, fmaxf(cl[m][0], cl[m][2]));
         mx1 = fmaxf(mx1, fmaxf(cl[m][1], cl[m][3]));
       }
@@ -392,7 +259,7 @@ __global__ void __launch_bounds__(PG_WARPS * 32) decode_paged_kernel(DecodeArgs 
     }
     __syncthreads();
     {
-      float *dst = a.partials + ((static_cast<int64_t>(bh) * P.n_slots + (P.has_sink + c)) * G + gt * 8) * PART;
+      float *dst = a.partials + ((static_cast<int64_t>(bh) * P.n_slots + (P.chunk_slot0 + c)) * G + gt * 8) * PART;
       for (int g = 0; g < g_valid; ++g) {
         float M = -INFINITY;
 #pragma unroll

@@ -2,10 +2,9 @@
 //
 // The plain kernel reduces any run of tiles — sink, packed pages, Q-buffers,
 // the rotated value ring — with one thread per token (logits) and one thread
-// per channel (output).  It always handles the sink tile and the tail of a
-// sequence, where full-precision rows dominate and the byte count is small
-// (a few hundred tokens per (batch, kv-head)); with impl=1 it handles the packed
-// pages too and serves as an in-library cross-check of the streaming kernel.
+// per channel (output).  It is slow and simple on purpose: with impl=1 it
+// computes a whole call and serves as an in-library cross-check of the streaming
+// and edge kernels.
 //
 // Dequantisation is `code * scale + min` evaluated in fp32 from the fp16
 // metadata (kernels/kitty_attention.py:162-165, 317-320 of the reference do it in
