@@ -8,7 +8,7 @@
 namespace kitty {
 
 constexpr int QS_ROW = HD + 8;   // halves per row of a staged query (row stride 272 B keeps rows 16-byte aligned)
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s: far beyond any healthy copy
 
 // ---- PTX wrappers --------------------------------------------------------- //
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -28,11 +28,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: false when the copy did not land within the limit.
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: false when the phase did not complete within WAIT_LIMIT_NS.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  return false;
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (global_ns() - t0 > WAIT_LIMIT_NS) return false;
+  }
 }
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
