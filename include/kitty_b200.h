@@ -148,8 +148,10 @@ int kitty_workspace_status(const void *workspace, int32_t *host_status, void *st
  * If partial_out is non-null the un-normalised result is written there instead
  * of `out`, as fp32 [B, h_q, 130] = (acc[128], running max, running sum) in the
  * base-2 domain, for kitty_lse_merge.
- * impl: 0 = default kernels; 1 = the plain CUDA-core kernel for every tile
- * (slow; kept as an in-library cross-check). */
+ * impl: 0 = default kernels (int8 tensor-core streaming kernel for groups of up
+ * to 4 query heads per KV head, fp16 tensor-core streaming kernel otherwise);
+ * 2 = the fp16 streaming kernel for every group size; 1 = the plain CUDA-core
+ * kernel for every tile (slow; kept as an in-library cross-check). */
 int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *counts, const void *query, int q_dtype,
                       int32_t B, int32_t h_q, float scaling, void *out, int out_dtype, void *workspace,
                       int64_t workspace_bytes, int32_t page_begin, int32_t page_end, int32_t flags,

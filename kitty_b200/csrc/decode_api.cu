@@ -83,7 +83,7 @@ extern "C" int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *c
   const int G = h_q / H;
   if (G > MAX_GROUP) return KITTY_E_BADSHAPE;
   if (q_dtype < KITTY_F16 || q_dtype > KITTY_F32 || out_dtype < KITTY_F16 || out_dtype > KITTY_F32) return KITTY_E_BADARG;
-  if (impl != 0 && impl != 1) return KITTY_E_BADARG;
+  if (impl < 0 || impl > 2) return KITTY_E_BADARG;
   if (B > 65535 || H > 65535) return KITTY_E_BADARG;
   const kitty_counts &C = *counts;
   if (C.PageCount_K < 0 || C.PageCount_V < 0 || C.PageCount_K > layer->max_page || C.PageCount_V > layer->max_page ||
@@ -108,10 +108,11 @@ extern "C" int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *c
   P.n_tiles = 1 + static_cast<int>((tk + PAGE - 1) / PAGE);
   P.has_sink = ((flags & 1) && C.Sink_Count > 0) ? 1 : 0;
   P.has_tail = ((flags & 2) && (P.n_tiles - 1 - pv) > 0) ? 1 : 0;
-  const int n_gt = (G + 7) / 8;
+  const bool use_i8 = (impl == 0 && G <= 4);       // integer tensor-core kernel: 4 heads x (high, low) limb columns
+  const int n_gt = use_i8 ? 1 : (G + 7) / 8;
   const int grid_max = 2 * sm_count();
   plan_chunks(P.pe - P.pb, static_cast<int64_t>(B) * H * n_gt, grid_max, &P.ch, &P.nchunk);
-  P.fast_chunks = (impl == 0) ? 1 : 0;
+  P.fast_chunks = (impl != 1) ? 1 : 0;
   const int has_edge = (P.has_sink || P.has_tail) ? 1 : 0;
   if (P.fast_chunks) {            // slots: [edge?][chunks]
     P.n_slots = has_edge + P.nchunk;
@@ -136,7 +137,11 @@ extern "C" int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *c
   if (P.fast_chunks && P.nchunk > 0) {
     const int64_t items = static_cast<int64_t>(B) * H * n_gt * P.nchunk;
     const int grid = static_cast<int>(std::min<int64_t>(items, grid_max));
-    if (int rc = launch_decode_paged(a, static_cast<int>(items), n_gt, grid, s)) return rc;
+    if (use_i8) {
+      if (int rc = launch_decode_paged_i8(a, static_cast<int>(items), grid, s)) return rc;
+    } else {
+      if (int rc = launch_decode_paged(a, static_cast<int>(items), n_gt, grid, s)) return rc;
+    }
   }
   if (P.fast_chunks) {
     if (has_edge)

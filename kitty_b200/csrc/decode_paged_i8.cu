@@ -1,0 +1,496 @@
+// Streaming decode attention over the common packed pages for query groups of up
+// to 4 heads per KV head — the integer tensor-core variant of the hot loop.
+//
+// Data path: as in the fp16 kernel.  Each warp owns a private two-stage ring of
+// page pairs in shared memory, filled by bulk async copies (cp.async.bulk +
+// mbarrier); the 10368 bytes of a pair are fetched from HBM exactly once.
+//
+// Arithmetic: mma.sync.m16n8k32 on 8-bit integers.
+//  * A operand = the packed codes themselves.  Four words of the record (four
+//    channels x 16 tokens for keys, four tokens x 16 channels for values) are
+//    byte-transposed with 8 PRMT so that a register holds the same byte of four
+//    contraction indices; `reg & (0x03030303 << 2r)` is then an A register: the
+//    u8 values code * 4^r of one token (channel) for four contraction indices —
+//    four fields per logic instruction, no shifts.
+//  * B operand = the small vector (q*scale for keys, p*scale for values) in
+//    16-bit fixed point, split into a high and a low 8-bit limb.  The 8 columns
+//    of the tile are (head, limb) for 4 heads, so one mma covers both limbs and
+//    every tensor-core column does useful work; hi*256 + lo is recombined in the
+//    fp32 epilogue together with the power-of-two weight 4^-r and the page's
+//    fixed-point scale.  Conversion to fixed point is a fused multiply-add with
+//    the magic constant 1.5*2^23 (the integer lands in the mantissa).
+//  * The rank-1 terms (sum q*min, sum p*zero, sum p) are a few fp32 FMAs per lane.
+// Per page pair and warp: 72 mma.sync and roughly 1000 other instructions, about
+// 600 of them on the integer/logic pipe.
+//
+// Every wait on an mbarrier is bounded; when one runs out the warp sets the
+// workspace's status word, stops consuming and the call's result is invalid.
+#include "paged_core.cuh"
+
+namespace kitty {
+
+constexpr int I8_WARPS = 4;
+constexpr int I8_STAGES = 2;
+constexpr int I8_OFF_KREC = 0;
+constexpr int I8_OFF_KMETA = K_HEAD;                      // 5248
+constexpr int I8_OFF_VREC = I8_OFF_KMETA + META_HEAD;     // 5760
+constexpr int I8_OFF_VMETA = I8_OFF_VREC + V_HEAD;        // 9856
+constexpr int I8_STAGE_BYTES = I8_OFF_VMETA + META_HEAD;  // 10368
+constexpr float KFIX = 8000.0f;     // |q^ * scale'| <= KFIX; the high plane uses 4x that, still inside int16
+constexpr float VFIX = 60000.0f;    // p * scale' <= VFIX < 2^16 (unsigned limbs)
+constexpr float MAGIC_S = 12582912.0f;   // 1.5 * 2^23: signed integers in the low mantissa bits
+constexpr float MAGIC_U = 8388608.0f;    // 2^23: unsigned integers in the low mantissa bits
+
+// Per-channel / per-token arrays are kept in "arranged" order so that the 8
+// values one lane needs for a k-step are contiguous:
+//   position(c) = (c >> 5) * 32 + (c & 3) * 8 + ((c >> 4) & 1) * 4 + ((c >> 2) & 3)
+// i.e. k-step ks, thread-in-group tg reads positions ks*32 + tg*8 + {0..3} (contraction bytes
+// 4*tg + i  <->  index 32*ks + tg + 4*i) and + {4..7} (bytes 16 + 4*tg + i  <->  32*ks + 16 + tg + 4*i).
+struct I8Warp {
+  __align__(128) uint8_t stage[I8_STAGES][I8_STAGE_BYTES];
+  __align__(16) float sarr[HD];        // keys: scale' per channel (arranged); values: scale' per token (plain)
+  __align__(16) float marr[HD];        // keys: min per channel (arranged);    values: zero-point per token (plain)
+  __align__(16) uint32_t pb[256];      // probabilities * scale' as limb bytes: [head*2 + limb][k-step][quad][tg] words
+  __align__(8) unsigned long long bar[I8_STAGES];
+  uint8_t inv[DB];                     // slot -> arranged position of its channel
+};
+
+struct I8Smem {
+  I8Warp w[I8_WARPS];
+  __align__(16) float qarr[4][HD];     // query / qmax per head, arranged
+  float qmax[4];
+};
+static_assert(I8_WARPS * 4 * PART * 4 <= I8_STAGE_BYTES * I8_STAGES, "merge buffer overlays warp 0's stages");
+
+__device__ __forceinline__ void imma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void imma_u8u8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// 4x4 byte transpose: t[j] = (w0.byte j, w1.byte j, w2.byte j, w3.byte j).
+__device__ __forceinline__ void transpose4(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, uint32_t (&t)[4]) {
+  const uint32_t lo01 = __byte_perm(w0, w1, 0x5140), hi01 = __byte_perm(w0, w1, 0x7362);
+  const uint32_t lo23 = __byte_perm(w2, w3, 0x5140), hi23 = __byte_perm(w2, w3, 0x7362);
+  t[0] = __byte_perm(lo01, lo23, 0x5410);
+  t[1] = __byte_perm(lo01, lo23, 0x7632);
+  t[2] = __byte_perm(hi01, hi23, 0x5410);
+  t[3] = __byte_perm(hi01, hi23, 0x7632);
+}
+
+// Four fixed-point values -> one B register holding their limb bytes.  sel picks the byte
+// (0x0040: byte 0 of both sources, 0x0051: byte 1 of both sources).
+__device__ __forceinline__ uint32_t pack_limb(float y0, float y1, float y2, float y3, uint32_t sel) {
+  const uint32_t p01 = __byte_perm(__float_as_uint(y0), __float_as_uint(y1), sel);
+  const uint32_t p23 = __byte_perm(__float_as_uint(y2), __float_as_uint(y3), sel);
+  return __byte_perm(p01, p23, 0x5410);
+}
+
+// One k-step of 32 contraction indices against 128 rows, rows = 16*gid + {0..15} of each lane.
+// words: base of the record's 32-bit words; the word of contraction index x and row group gid
+// is words[x * 8 + gid].  idx0: first contraction index of the k-step; stride between the four
+// bytes of a quad is `step` indices.  Tiles mu = 4*jj + r: row gid <-> 16*gid + 4*jj + r,
+// row gid + 8 <-> 16*gid + 8 + 4*jj + r, weight 4^r.
+template <bool kSignedB>
+__device__ __forceinline__ void kstep32(const uint32_t *words, int gid, int idxA, int idxB, int step, uint32_t b0,
+                                        uint32_t b1, int (&c)[8][4]) {
+  uint32_t ta[4], tb[4];
+  transpose4(words[(idxA)*8 + gid], words[(idxA + step) * 8 + gid], words[(idxA + 2 * step) * 8 + gid],
+             words[(idxA + 3 * step) * 8 + gid], ta);
+  transpose4(words[(idxB)*8 + gid], words[(idxB + step) * 8 + gid], words[(idxB + 2 * step) * 8 + gid],
+             words[(idxB + 3 * step) * 8 + gid], tb);
+#pragma unroll
+  for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const uint32_t msk = 0x03030303u << (2 * r);
+      if (kSignedB) imma_u8s8(c[4 * jj + r], ta[jj] & msk, ta[jj + 2] & msk, tb[jj] & msk, tb[jj + 2] & msk, b0, b1);
+      else imma_u8u8(c[4 * jj + r], ta[jj] & msk, ta[jj + 2] & msk, tb[jj] & msk, tb[jj + 2] & msk, b0, b1);
+    }
+}
+
+__global__ void __launch_bounds__(I8_WARPS * 32) decode_paged_i8_kernel(DecodeArgs a, int n_items) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  I8Smem &sm = *reinterpret_cast<I8Smem *>(smem_raw);
+  const DecodePlan &P = a.P;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int gid = lane >> 2, tig = lane & 3;
+  const int H = P.H, G = P.G;
+  I8Warp &ws = sm.w[warp];
+  const int colhead = gid >> 1;                                   // B column gid = (head, limb)
+  const bool hi_limb = (gid & 1) == 0;
+  const uint32_t limb_sel = hi_limb ? 0x0051u : 0x0040u;
+  const float kmagic = MAGIC_S + (hi_limb ? 128.0f : 0.0f);       // +128: rounds the low limb into the high one
+
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < I8_STAGES; ++s) mbar_init(smem_u32(&ws.bar[s]), 1);
+  }
+  ws.inv[lane] = 0;
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  __syncthreads();
+
+  uint32_t seq = 0;          // page pairs consumed by this warp so far (ring position and parity)
+  bool dead = false;         // a bounded wait ran out: stop consuming, keep the block barriers uniform
+  uint32_t inflight = 0;     // bit s: stage s has a copy in flight (warp-uniform)
+
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const int c = item % P.nchunk;
+    const int bh = item / P.nchunk;
+    const int h = bh % H, b = bh / H;
+    const int p0 = P.pb + c * P.ch;
+    const int p1 = min(P.pe, p0 + P.ch);
+
+    __syncthreads();   // previous item's merge buffer (overlaying warp 0's stages) and query are no longer read
+    // ---- query of head `warp`: maximum, then q / qmax in arranged order ---- //
+    {
+      float qv[4], mx = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int cch = 4 * lane + i;
+        qv[i] = (warp < G) ? load_q(a.q, a.q_dtype, (static_cast<int64_t>(b) * P.h_q + h * G + warp) * HD + cch) * a.scale_log2 : 0.f;
+        mx = fmaxf(mx, fabsf(qv[i]));
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      mx = fmaxf(mx, 1e-30f);
+      const float inv_mx = 1.0f / mx;
+      const int base = ((lane >> 3) << 5) + (lane & 7);          // arranged position of channel 4*lane + i is base + 8*i
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sm.qarr[warp][base + 8 * i] = qv[i] * inv_mx;
+      if (lane == 0) sm.qmax[warp] = mx;
+    }
+    // first copies of this warp: pages p0 + warp, p0 + warp + I8_WARPS, ...
+    const int first = p0 + warp;
+    if (!dead) {
+      if (lane == 0) {
+        // the stages may have been written through the generic proxy (merge buffer): order that before the bulk copies
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#pragma unroll
+        for (int s = 0; s < I8_STAGES; ++s) {
+          const int pg = first + s * I8_WARPS;
+          if (pg < p1) {
+            const uint32_t st = (seq + s) % I8_STAGES;
+            const uint32_t bar = smem_u32(&ws.bar[st]), dst = smem_u32(&ws.stage[st][0]);
+            const int64_t pk = a.L.PageTable_K[static_cast<int64_t>(b) * a.L.max_page + pg];
+            const int64_t pv = a.L.PageTable_V[static_cast<int64_t>(b) * a.L.max_page + pg];
+            mbar_expect_tx(bar, I8_STAGE_BYTES);
+            bulk_g2s(dst + I8_OFF_KREC, a.L.KeyCache + pk * (static_cast<int64_t>(H) * K_HEAD) + static_cast<int64_t>(h) * K_HEAD, K_HEAD, bar);
+            bulk_g2s(dst + I8_OFF_KMETA, static_cast<const uint8_t *>(a.L.KeyCache_metadata) + (pk * H + h) * META_HEAD, META_HEAD, bar);
+            bulk_g2s(dst + I8_OFF_VREC, a.L.ValueCache + pv * (static_cast<int64_t>(H) * V_HEAD) + static_cast<int64_t>(h) * V_HEAD, V_HEAD, bar);
+            bulk_g2s(dst + I8_OFF_VMETA, static_cast<const uint8_t *>(a.L.ValueCache_metadata) + (pv * H + h) * META_HEAD, META_HEAD, bar);
+          }
+        }
+      }
+#pragma unroll
+      for (int s = 0; s < I8_STAGES; ++s)
+        if (first + s * I8_WARPS < p1) inflight |= 1u << ((seq + s) % I8_STAGES);
+    }
+    __syncthreads();   // staged query visible
+
+    // This lane's output head is `tig` (accumulator columns 2*tig, 2*tig+1 = its high and low limb).
+    const float qmax_t = sm.qmax[tig];
+    float acc[8][2];       // out[channel 16*gid + 4*jj + r (+8)][head tig], tile mu = 4*jj + r
+#pragma unroll
+    for (int m = 0; m < 8; ++m) acc[m][0] = acc[m][1] = 0.f;
+    float zsum = 0.f, lsum = 0.f;      // this lane's share of sum p*zero-point and sum p (tokens 16*gid..16*gid+15, head tig)
+    float m_run = -INFINITY;
+
+    for (int pg = first; pg < p1 && !dead; pg += I8_WARPS) {
+      const uint32_t st = seq % I8_STAGES, parity = (seq / I8_STAGES) & 1u;
+      const uint32_t bar = smem_u32(&ws.bar[st]);
+      if (!mbar_wait(bar, parity)) { dead = true; break; }
+      inflight &= ~(1u << st);
+      const uint8_t *stg = ws.stage[st];
+      const uint32_t *kw = reinterpret_cast<const uint32_t *>(stg + I8_OFF_KREC);
+      const uint32_t *hw = reinterpret_cast<const uint32_t *>(stg + I8_OFF_KREC + K_OFF_HI);
+      const uint32_t *km = reinterpret_cast<const uint32_t *>(stg + I8_OFF_KMETA);
+      const uint32_t *vw = reinterpret_cast<const uint32_t *>(stg + I8_OFF_VREC);
+      const uint32_t *vm = reinterpret_cast<const uint32_t *>(stg + I8_OFF_VMETA);
+
+      // ---- key pre-pass: slot table, scale' = scale * KFIX / max scale and min, arranged ---- //
+      float k_unit;      // value of one fixed-point unit of q^ * scale
+      {
+        const uint32_t w = *reinterpret_cast<const uint32_t *>(stg + I8_OFF_KREC + K_OFF_IDX + 4 * lane);
+        const int base = ((lane >> 3) << 5) + (lane & 7);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t s = (w >> (8 * i)) & 0xffu;
+          if (s < DB) ws.inv[s] = static_cast<uint8_t>(base + 8 * i);
+        }
+        // arranged positions 4*lane .. 4*lane+3  <->  channels 32*ks + 16*quad + tg + 4*i
+        const int ch0 = ((lane >> 3) << 5) + ((lane & 1) << 4) + ((lane >> 1) & 3);
+        float sc[4], mn[4], smax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&km[ch0 + 4 * i]));
+          sc[i] = f.x;
+          mn[i] = f.y;
+          smax = fmaxf(smax, f.x);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) smax = fmaxf(smax, __shfl_xor_sync(0xffffffffu, smax, o));
+        const float fix = KFIX / smax;                     // scale >= 1e-6 by construction of the pages
+        k_unit = smax * (1.0f / KFIX);
+        *reinterpret_cast<float4 *>(&ws.sarr[4 * lane]) = make_float4(sc[0] * fix, sc[1] * fix, sc[2] * fix, sc[3] * fix);
+        *reinterpret_cast<float4 *>(&ws.marr[4 * lane]) = make_float4(mn[0], mn[1], mn[2], mn[3]);
+      }
+      __syncwarp();
+
+      // ================= Q K^T ================= //
+      int cl[8][4];      // [tile][hi row gid, lo row gid, hi row gid+8, lo row gid+8] of head tig
+#pragma unroll
+      for (int m = 0; m < 8; ++m) cl[m][0] = cl[m][1] = cl[m][2] = cl[m][3] = 0;
+      const float *qrow = sm.qarr[colhead];
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        const int pos = ks * 32 + tig * 8;
+        const float4 qa = *reinterpret_cast<const float4 *>(qrow + pos), qb = *reinterpret_cast<const float4 *>(qrow + pos + 4);
+        const float4 sa = *reinterpret_cast<const float4 *>(&ws.sarr[pos]), sb = *reinterpret_cast<const float4 *>(&ws.sarr[pos + 4]);
+        const uint32_t b0 = pack_limb(fmaf(qa.x, sa.x, kmagic), fmaf(qa.y, sa.y, kmagic), fmaf(qa.z, sa.z, kmagic),
+                                      fmaf(qa.w, sa.w, kmagic), limb_sel);
+        const uint32_t b1 = pack_limb(fmaf(qb.x, sb.x, kmagic), fmaf(qb.y, sb.y, kmagic), fmaf(qb.z, sb.z, kmagic),
+                                      fmaf(qb.w, sb.w, kmagic), limb_sel);
+        kstep32<true>(kw, gid, 32 * ks + tig, 32 * ks + 16 + tig, 4, b0, b1, cl);
+      }
+      // high plane: 32 slots = one k-step; bytes 4*tig + i <-> slot 4*tig + i, bytes 16 + 4*tig + i <-> slot 16 + 4*tig + i;
+      // operand = 4 * q^ * scale' of the slot's channel
+      {
+        const uint32_t ia = *reinterpret_cast<const uint32_t *>(&ws.inv[4 * tig]);
+        const uint32_t ib = *reinterpret_cast<const uint32_t *>(&ws.inv[16 + 4 * tig]);
+        float ya[4], yb[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int pa = (ia >> (8 * i)) & 0xff, pb2 = (ib >> (8 * i)) & 0xff;
+          ya[i] = fmaf(qrow[pa] * 4.0f, ws.sarr[pa], kmagic);
+          yb[i] = fmaf(qrow[pb2] * 4.0f, ws.sarr[pb2], kmagic);
+        }
+        const uint32_t b0 = pack_limb(ya[0], ya[1], ya[2], ya[3], limb_sel);
+        const uint32_t b1 = pack_limb(yb[0], yb[1], yb[2], yb[3], limb_sel);
+        kstep32<true>(hw, gid, 4 * tig, 16 + 4 * tig, 1, b0, b1, cl);
+      }
+      // sum_c q*min for head tig: this lane covers arranged positions 16*gid .. 16*gid+15
+      float bias = 0.f;
+      {
+        const float *qt = sm.qarr[tig] + 16 * gid;
+#pragma unroll
+        for (int v4 = 0; v4 < 4; ++v4) {
+          const float4 qq = *reinterpret_cast<const float4 *>(qt + 4 * v4);
+          const float4 mm = *reinterpret_cast<const float4 *>(&ws.marr[16 * gid + 4 * v4]);
+          bias = fmaf(qq.x, mm.x, bias);
+          bias = fmaf(qq.y, mm.y, bias);
+          bias = fmaf(qq.z, mm.z, bias);
+          bias = fmaf(qq.w, mm.w, bias);
+        }
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) bias += __shfl_xor_sync(0xffffffffu, bias, o);
+        bias *= qmax_t;
+      }
+
+      // ---- value pre-pass (plain token order): scale' = scale * VFIX / max scale, zero-point ---- //
+      float v_unit;
+      {
+        float sc[4], zp[4], smax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&vm[4 * lane + i]));
+          sc[i] = f.x;
+          zp[i] = f.y;
+          smax = fmaxf(smax, f.x);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) smax = fmaxf(smax, __shfl_xor_sync(0xffffffffu, smax, o));
+        const float fix = VFIX / smax;
+        v_unit = smax * (1.0f / VFIX);
+        __syncwarp();                                      // every lane has read the key scales and mins
+        *reinterpret_cast<float4 *>(&ws.sarr[4 * lane]) = make_float4(sc[0] * fix, sc[1] * fix, sc[2] * fix, sc[3] * fix);
+        *reinterpret_cast<float4 *>(&ws.marr[4 * lane]) = make_float4(zp[0], zp[1], zp[2], zp[3]);
+      }
+
+      // ================= online softmax: 16 tokens (16*gid + e) of head tig per lane ================= //
+      // e = 8*h8 + 4*jj + r  <->  cl[4*jj + r][2*h8 (hi), 2*h8 + 1 (lo)]
+      float lg[16];
+      {
+        const float u0 = k_unit * qmax_t;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            const float u = u0 * (1.0f / static_cast<float>(1 << (2 * r)));
+#pragma unroll
+            for (int h8 = 0; h8 < 2; ++h8) {
+              const int d = cl[4 * jj + r][2 * h8] * 256 + cl[4 * jj + r][2 * h8 + 1];
+              const float v = fmaf(static_cast<float>(d), u, bias);
+              lg[8 * h8 + 4 * jj + r] = v;
+              mx = fmaxf(mx, v);
+            }
+          }
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const float mnew = fmaxf(m_run, mx);
+        const float alpha = (m_run == -INFINITY) ? 0.f : ex2(m_run - mnew);
+        m_run = mnew;
+#pragma unroll
+        for (int m = 0; m < 8; ++m) {
+          acc[m][0] *= alpha;
+          acc[m][1] *= alpha;
+        }
+        zsum *= alpha;
+        lsum *= alpha;
+      }
+      __syncwarp();      // value scales / zero-points visible
+      {
+        float y[16];
+#pragma unroll
+        for (int v4 = 0; v4 < 4; ++v4) {
+          const float4 s4 = *reinterpret_cast<const float4 *>(&ws.sarr[16 * gid + 4 * v4]);
+          const float4 z4 = *reinterpret_cast<const float4 *>(&ws.marr[16 * gid + 4 * v4]);
+          const float sv[4] = {s4.x, s4.y, s4.z, s4.w}, zv[4] = {z4.x, z4.y, z4.z, z4.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float p = ex2(lg[4 * v4 + i] - m_run);
+            lsum += p;
+            zsum = fmaf(p, zv[i], zsum);
+            y[4 * v4 + i] = fmaf(p, sv[i], MAGIC_U);
+          }
+        }
+        // limb bytes: word tg of limb block = tokens e = tg + 4*i (i = 0..3); both limbs from one pair of PRMTs
+        uint32_t whi[4], wlo[4];
+#pragma unroll
+        for (int tg = 0; tg < 4; ++tg) {
+          const uint32_t pab = __byte_perm(__float_as_uint(y[tg]), __float_as_uint(y[tg + 4]), 0x5140);        // (a.b0, b.b0, a.b1, b.b1)
+          const uint32_t pcd = __byte_perm(__float_as_uint(y[tg + 8]), __float_as_uint(y[tg + 12]), 0x5140);
+          wlo[tg] = __byte_perm(pab, pcd, 0x5410);
+          whi[tg] = __byte_perm(pab, pcd, 0x7632);
+        }
+        // pb word index = (head*2 + limb)*32 + ks*8 + quad*4 + tg, tokens 16*gid.. <-> ks = gid >> 1, quad = gid & 1
+        uint32_t *dst = ws.pb + (2 * tig) * 32 + (gid >> 1) * 8 + (gid & 1) * 4;
+        *reinterpret_cast<uint4 *>(dst) = make_uint4(whi[0], whi[1], whi[2], whi[3]);
+        *reinterpret_cast<uint4 *>(dst + 32) = make_uint4(wlo[0], wlo[1], wlo[2], wlo[3]);
+      }
+      __syncwarp();
+
+      // ================= P V ================= //
+      // rows = channels 16*gid + {0..15}; contraction bytes 4*tig + i <-> token 32*ks + tig + 4*i, 16 + 4*tig + i <-> +16
+      int cv[8][4];
+#pragma unroll
+      for (int m = 0; m < 8; ++m) cv[m][0] = cv[m][1] = cv[m][2] = cv[m][3] = 0;
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        const uint32_t b0 = ws.pb[gid * 32 + ks * 8 + tig], b1 = ws.pb[gid * 32 + ks * 8 + 4 + tig];
+        kstep32<false>(vw, gid, 32 * ks + tig, 32 * ks + 16 + tig, 4, b0, b1, cv);
+      }
+      {
+        const float u0 = v_unit;
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            const float u = u0 * (1.0f / static_cast<float>(1 << (2 * r)));
+            const int m = 4 * jj + r;
+            acc[m][0] = fmaf(static_cast<float>(cv[m][0] * 256 + cv[m][1]), u, acc[m][0]);
+            acc[m][1] = fmaf(static_cast<float>(cv[m][2] * 256 + cv[m][3]), u, acc[m][1]);
+          }
+      }
+      __syncwarp();      // every lane is done with this stage and with the warp's buffers
+      ++seq;
+      const int nxt = pg + I8_STAGES * I8_WARPS;
+      if (nxt < p1) {
+        if (lane == 0) {
+          const uint32_t dst = smem_u32(&ws.stage[st][0]);
+          const int64_t pk = a.L.PageTable_K[static_cast<int64_t>(b) * a.L.max_page + nxt];
+          const int64_t pv = a.L.PageTable_V[static_cast<int64_t>(b) * a.L.max_page + nxt];
+          mbar_expect_tx(bar, I8_STAGE_BYTES);
+          bulk_g2s(dst + I8_OFF_KREC, a.L.KeyCache + pk * (static_cast<int64_t>(H) * K_HEAD) + static_cast<int64_t>(h) * K_HEAD, K_HEAD, bar);
+          bulk_g2s(dst + I8_OFF_KMETA, static_cast<const uint8_t *>(a.L.KeyCache_metadata) + (pk * H + h) * META_HEAD, META_HEAD, bar);
+          bulk_g2s(dst + I8_OFF_VREC, a.L.ValueCache + pv * (static_cast<int64_t>(H) * V_HEAD) + static_cast<int64_t>(h) * V_HEAD, V_HEAD, bar);
+          bulk_g2s(dst + I8_OFF_VMETA, static_cast<const uint8_t *>(a.L.ValueCache_metadata) + (pv * H + h) * META_HEAD, META_HEAD, bar);
+        }
+        inflight |= 1u << st;
+      }
+    }
+
+    if (dead) {
+      if (lane == 0) atomicExch(a.status, 1);
+      // give copies still in flight a bounded time to land before the stages are reused or the block exits
+      for (int s = 0; s < I8_STAGES; ++s)
+        if (inflight & (1u << s)) {
+          const uint32_t nseq = seq + ((s + I8_STAGES - seq % I8_STAGES) % I8_STAGES);
+          mbar_wait(smem_u32(&ws.bar[s]), (nseq / I8_STAGES) & 1u);
+          inflight &= ~(1u << s);
+        }
+    }
+    // sum p*zero and sum p over all tokens of the warp's pages: add the 8 row groups
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+      zsum += __shfl_xor_sync(0xffffffffu, zsum, o);
+      lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+    }
+    __syncthreads();     // all warps have consumed every copy they issued: warp 0's stages can be overlaid
+
+    // ---- warp result -> merge buffer [warp][head][PART] ---- //
+    float *mb = reinterpret_cast<float *>(&sm.w[0].stage[0][0]);
+    {
+      float *w = mb + (warp * 4 + tig) * PART;
+#pragma unroll
+      for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          w[16 * gid + 4 * jj + r] = acc[4 * jj + r][0] + zsum;
+          w[16 * gid + 8 + 4 * jj + r] = acc[4 * jj + r][1] + zsum;
+        }
+      if (gid == 0) {
+        w[HD] = m_run;
+        w[HD + 1] = lsum;
+      }
+    }
+    __syncthreads();
+    {
+      float *dst = a.partials + ((static_cast<int64_t>(bh) * P.n_slots + (P.chunk_slot0 + c)) * G) * PART;
+      for (int g = 0; g < G; ++g) {
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < I8_WARPS; ++w) M = fmaxf(M, mb[(w * 4 + g) * PART + HD]);
+        float A = 0.f, Ls = 0.f;
+#pragma unroll
+        for (int w = 0; w < I8_WARPS; ++w) {
+          const float mw = mb[(w * 4 + g) * PART + HD];
+          const float wt = (mw == -INFINITY) ? 0.f : ex2(mw - M);
+          A = fmaf(mb[(w * 4 + g) * PART + tid], wt, A);
+          Ls = fmaf(mb[(w * 4 + g) * PART + HD + 1], wt, Ls);
+        }
+        dst[g * PART + tid] = A;
+        if (tid == 0) {
+          dst[g * PART + HD] = M;
+          dst[g * PART + HD + 1] = Ls;
+        }
+      }
+    }
+  }
+}
+
+int launch_decode_paged_i8(const DecodeArgs &a, int n_items, int grid, cudaStream_t s) {
+  static int configured = -1;     // per-process opt-in to > 48 KB dynamic shared memory, done once per device
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return KITTY_E_CUDA;
+  if (configured != dev) {
+    if (cudaFuncSetAttribute(decode_paged_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(sizeof(I8Smem))) != cudaSuccess)
+      return KITTY_E_CUDA;
+    configured = dev;
+  }
+  decode_paged_i8_kernel<<<grid, I8_WARPS * 32, sizeof(I8Smem), s>>>(a, n_items);
+  return cudaGetLastError() == cudaSuccess ? KITTY_OK : KITTY_E_CUDA;
+}
+
+}  // namespace kitty

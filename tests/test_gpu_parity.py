@@ -185,8 +185,9 @@ def test_cache_replay_against_oracle_and_reference(kb, name):
             assert w is None and out.shape == (B, 1, h_q, D) and out.dtype == torch.float16
             want = ko.decode_attention(olay, q, h_q, scaling)
             assert ko.rel_err(out.float().cpu().numpy(), want) <= ATTN_TOL
-            out1 = kb.decode_attention(q.to(DEV), lay, H, scaling, impl=1)
-            assert ko.rel_err(out1.float().cpu().numpy(), want) <= ATTN_TOL
+            for impl in (1, 2):
+                out1 = kb.decode_attention(q.to(DEV), lay, H, scaling, impl=impl)
+                assert ko.rel_err(out1.float().cpu().numpy(), want) <= ATTN_TOL
             if s in probes:
                 ref = ko.as_f32(tensor_from_raw(fx["attn_out"][probes.index(s)], "f16"))
                 assert ko.rel_err(out.float().cpu().numpy(), ref) <= ATTN_TOL
@@ -234,7 +235,7 @@ def test_attention_after_prefill_and_a_few_steps(kb, h_kv, h_q, B, L, dtype):
         cache.update(kt.to(DEV), vt.to(DEV), 0)
         ocache.update(kt, vt, 0, dtype=dn)
         want = ko.decode_attention(olay, q, h_q, scaling)
-        for impl in (0, 1):
+        for impl in (0, 1, 2):      # default kernels, plain cross-check kernel, fp16 streaming kernel
             out = kb.decode_attention(q.to(DEV), lay, h_kv, scaling, impl=impl)
             assert out.dtype == dtype
             err = ko.rel_err(out.float().cpu().numpy(), want)
@@ -328,6 +329,8 @@ def test_full_size_32k_properties(kb):
     fast = kb.decode_attention(q, lay, h_kv, sc).float().cpu().numpy()
     plain = kb.decode_attention(q, lay, h_kv, sc, impl=1).float().cpu().numpy()
     assert ko.rel_err(fast, plain) <= ATTN_TOL
+    fp16k = kb.decode_attention(q, lay, h_kv, sc, impl=2).float().cpu().numpy()
+    assert ko.rel_err(fp16k, plain) <= ATTN_TOL
     parts = torch.empty(4, B, h_q, 130, dtype=torch.float32, device=DEV)
     cuts = [0, 64, 128, 192, 254]
     for r in range(4):
