@@ -63,9 +63,9 @@ extern "C" int64_t kitty_decode_workspace_bytes(int32_t B, int32_t h_kv, int32_t
   const int G = h_q / h_kv;
   if (G > MAX_GROUP) return KITTY_E_BADSHAPE;
   const int n_gt = (G + 7) / 8;
-  const int grid_max = 2 * sm_count();
+  const int grid_max = 4 * sm_count();                        // the larger of the two streaming kernels' resident grids
   const int64_t bh = static_cast<int64_t>(B) * h_kv;
-  int cap = chunk_cap(bh * n_gt, grid_max);
+  int cap = chunk_cap(bh, grid_max);                          // >= the cap any kernel choice uses
   cap = std::min(cap, std::max(1, (max_pages + PG_WARPS_HOST - 1) / PG_WARPS_HOST));
   return WS_HEADER + bh * (cap + 2) * G * PART * static_cast<int64_t>(sizeof(float));
 }
@@ -110,7 +110,7 @@ extern "C" int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *c
   P.has_tail = ((flags & 2) && (P.n_tiles - 1 - pv) > 0) ? 1 : 0;
   const bool use_i8 = (impl == 0 && G <= 4);       // integer tensor-core kernel: 4 heads x (high, low) limb columns
   const int n_gt = use_i8 ? 1 : (G + 7) / 8;
-  const int grid_max = 2 * sm_count();
+  const int grid_max = (use_i8 ? 4 : 2) * sm_count();        // resident blocks per SM of the streaming kernel
   plan_chunks(P.pe - P.pb, static_cast<int64_t>(B) * H * n_gt, grid_max, &P.ch, &P.nchunk);
   P.fast_chunks = (impl != 1) ? 1 : 0;
   const int has_edge = (P.has_sink || P.has_tail) ? 1 : 0;

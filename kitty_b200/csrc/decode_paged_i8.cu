@@ -1,9 +1,14 @@
 // Streaming decode attention over the common packed pages for query groups of up
 // to 4 heads per KV head — the integer tensor-core variant of the hot loop.
 //
-// Data path: as in the fp16 kernel.  Each warp owns a private two-stage ring of
-// page pairs in shared memory, filled by bulk async copies (cp.async.bulk +
-// mbarrier); the 10368 bytes of a pair are fetched from HBM exactly once.
+// Data path.  Each warp owns one shared-memory stage with a key part (record
+// 5248 B + metadata 512 B) and a value part (4096 B + 512 B), each filled by bulk
+// async copies (cp.async.bulk) that complete on the part's own mbarrier.  As soon
+// as the warp has consumed the key part of page i it requests the key part of its
+// next page, which lands while the warp does softmax and P V; the value part is
+// re-requested after P V and lands during the next Q K^T.  One stage per warp keeps
+// shared memory at ~13 KB per warp, so 16 warps (4 blocks) are resident per SM.
+// The 10368 bytes of a page pair are fetched from HBM exactly once.
 //
 // Arithmetic: mma.sync.m16n8k32 on 8-bit integers.
 //  * A operand = the packed codes themselves.  Four words of the record (four
@@ -30,7 +35,10 @@
 namespace kitty {
 
 constexpr int I8_WARPS = 4;
-constexpr int I8_STAGES = 2;
+constexpr int I8_KPART = K_HEAD + META_HEAD;              // 5760
+constexpr int I8_VPART = V_HEAD + META_HEAD;              // 4608
+constexpr int PB_RS = 36;                                 // words per (head, limb) row of the probability buffer (32 + pad)
+constexpr int QROW = HD + 4;                              // floats per row of the arranged query (pad against bank conflicts)
 constexpr int I8_OFF_KREC = 0;
 constexpr int I8_OFF_KMETA = K_HEAD;                      // 5248
 constexpr int I8_OFF_VREC = I8_OFF_KMETA + META_HEAD;     // 5760
@@ -47,20 +55,20 @@ constexpr float MAGIC_U = 8388608.0f;    // 2^23: unsigned integers in the low m
 // i.e. k-step ks, thread-in-group tg reads positions ks*32 + tg*8 + {0..3} (contraction bytes
 // 4*tg + i  <->  index 32*ks + tg + 4*i) and + {4..7} (bytes 16 + 4*tg + i  <->  32*ks + 16 + tg + 4*i).
 struct I8Warp {
-  __align__(128) uint8_t stage[I8_STAGES][I8_STAGE_BYTES];
+  __align__(128) uint8_t stage[I8_STAGE_BYTES];
   __align__(16) float sarr[HD];        // keys: scale' per channel (arranged); values: scale' per token (plain)
   __align__(16) float marr[HD];        // keys: min per channel (arranged);    values: zero-point per token (plain)
-  __align__(16) uint32_t pb[256];      // probabilities * scale' as limb bytes: [head*2 + limb][k-step][quad][tg] words
-  __align__(8) unsigned long long bar[I8_STAGES];
+  __align__(16) uint32_t pb[8 * PB_RS]; // probabilities * scale' as limb bytes: [head*2 + limb][k-step][quad][tg] words
+  __align__(8) unsigned long long bar_k, bar_v;
   uint8_t inv[DB];                     // slot -> arranged position of its channel
 };
 
 struct I8Smem {
   I8Warp w[I8_WARPS];
-  __align__(16) float qarr[4][HD];     // query / qmax per head, arranged
+  __align__(16) float qarr[4][QROW];   // query / qmax per head, arranged
   float qmax[4];
 };
-static_assert(I8_WARPS * 4 * PART * 4 <= I8_STAGE_BYTES * I8_STAGES, "merge buffer overlays warp 0's stages");
+static_assert(I8_WARPS * 4 * PART * 4 <= I8_STAGE_BYTES, "merge buffer overlays warp 0's stage");
 
 __device__ __forceinline__ void imma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                           uint32_t b1) {
@@ -118,7 +126,22 @@ __device__ __forceinline__ void kstep32(const uint32_t *words, int gid, int idxA
     }
 }
 
-__global__ void __launch_bounds__(I8_WARPS * 32) decode_paged_i8_kernel(DecodeArgs a, int n_items) {
+__device__ __forceinline__ void i8_issue_k(const DecodeArgs &a, int b, int h, int page, uint32_t dst, uint32_t bar) {
+  const int H = a.P.H;
+  const int64_t pk = a.L.PageTable_K[static_cast<int64_t>(b) * a.L.max_page + page];
+  mbar_expect_tx(bar, I8_KPART);
+  bulk_g2s(dst + I8_OFF_KREC, a.L.KeyCache + pk * (static_cast<int64_t>(H) * K_HEAD) + static_cast<int64_t>(h) * K_HEAD, K_HEAD, bar);
+  bulk_g2s(dst + I8_OFF_KMETA, static_cast<const uint8_t *>(a.L.KeyCache_metadata) + (pk * H + h) * META_HEAD, META_HEAD, bar);
+}
+__device__ __forceinline__ void i8_issue_v(const DecodeArgs &a, int b, int h, int page, uint32_t dst, uint32_t bar) {
+  const int H = a.P.H;
+  const int64_t pv = a.L.PageTable_V[static_cast<int64_t>(b) * a.L.max_page + page];
+  mbar_expect_tx(bar, I8_VPART);
+  bulk_g2s(dst + I8_OFF_VREC, a.L.ValueCache + pv * (static_cast<int64_t>(H) * V_HEAD) + static_cast<int64_t>(h) * V_HEAD, V_HEAD, bar);
+  bulk_g2s(dst + I8_OFF_VMETA, static_cast<const uint8_t *>(a.L.ValueCache_metadata) + (pv * H + h) * META_HEAD, META_HEAD, bar);
+}
+
+__global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(DecodeArgs a, int n_items) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   I8Smem &sm = *reinterpret_cast<I8Smem *>(smem_raw);
   const DecodePlan &P = a.P;
@@ -132,16 +155,17 @@ __global__ void __launch_bounds__(I8_WARPS * 32) decode_paged_i8_kernel(DecodeAr
   const float kmagic = MAGIC_S + (hi_limb ? 128.0f : 0.0f);       // +128: rounds the low limb into the high one
 
   if (lane == 0) {
-#pragma unroll
-    for (int s = 0; s < I8_STAGES; ++s) mbar_init(smem_u32(&ws.bar[s]), 1);
+    mbar_init(smem_u32(&ws.bar_k), 1);
+    mbar_init(smem_u32(&ws.bar_v), 1);
   }
   ws.inv[lane] = 0;
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   __syncthreads();
 
-  uint32_t seq = 0;          // page pairs consumed by this warp so far (ring position and parity)
+  uint32_t seq = 0;          // page pairs consumed by this warp so far (mbarrier parity)
   bool dead = false;         // a bounded wait ran out: stop consuming, keep the block barriers uniform
-  uint32_t inflight = 0;     // bit s: stage s has a copy in flight (warp-uniform)
+  uint32_t inflight = 0;     // bit 0: a key-part copy is in flight, bit 1: a value-part copy (warp-uniform)
+  const uint32_t bar_k = smem_u32(&ws.bar_k), bar_v = smem_u32(&ws.bar_v), stage_u32 = smem_u32(&ws.stage[0]);
 
   for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
     const int c = item % P.nchunk;
@@ -150,7 +174,7 @@ __global__ void __launch_bounds__(I8_WARPS * 32) decode_paged_i8_kernel(DecodeAr
     const int p0 = P.pb + c * P.ch;
     const int p1 = min(P.pe, p0 + P.ch);
 
-    __syncthreads();   // previous item's merge buffer (overlaying warp 0's stages) and query are no longer read
+    __syncthreads();   // previous item's merge buffer (overlaying warp 0's stage) and query are no longer read
     // ---- query of head `warp`: maximum, then q / qmax in arranged order ---- //
     {
       float qv[4], mx = 0.f;
@@ -169,31 +193,16 @@ __global__ void __launch_bounds__(I8_WARPS * 32) decode_paged_i8_kernel(DecodeAr
       for (int i = 0; i < 4; ++i) sm.qarr[warp][base + 8 * i] = qv[i] * inv_mx;
       if (lane == 0) sm.qmax[warp] = mx;
     }
-    // first copies of this warp: pages p0 + warp, p0 + warp + I8_WARPS, ...
+    // this warp's pages: p0 + warp, p0 + warp + I8_WARPS, ...
     const int first = p0 + warp;
-    if (!dead) {
+    if (!dead && first < p1) {
       if (lane == 0) {
-        // the stages may have been written through the generic proxy (merge buffer): order that before the bulk copies
+        // the stage may have been written through the generic proxy (merge buffer): order that before the bulk copies
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-#pragma unroll
-        for (int s = 0; s < I8_STAGES; ++s) {
-          const int pg = first + s * I8_WARPS;
-          if (pg < p1) {
-            const uint32_t st = (seq + s) % I8_STAGES;
-            const uint32_t bar = smem_u32(&ws.bar[st]), dst = smem_u32(&ws.stage[st][0]);
-            const int64_t pk = a.L.PageTable_K[static_cast<int64_t>(b) * a.L.max_page + pg];
-            const int64_t pv = a.L.PageTable_V[static_cast<int64_t>(b) * a.L.max_page + pg];
-            mbar_expect_tx(bar, I8_STAGE_BYTES);
-            bulk_g2s(dst + I8_OFF_KREC, a.L.KeyCache + pk * (static_cast<int64_t>(H) * K_HEAD) + static_cast<int64_t>(h) * K_HEAD, K_HEAD, bar);
-            bulk_g2s(dst + I8_OFF_KMETA, static_cast<const uint8_t *>(a.L.KeyCache_metadata) + (pk * H + h) * META_HEAD, META_HEAD, bar);
-            bulk_g2s(dst + I8_OFF_VREC, a.L.ValueCache + pv * (static_cast<int64_t>(H) * V_HEAD) + static_cast<int64_t>(h) * V_HEAD, V_HEAD, bar);
-            bulk_g2s(dst + I8_OFF_VMETA, static_cast<const uint8_t *>(a.L.ValueCache_metadata) + (pv * H + h) * META_HEAD, META_HEAD, bar);
-          }
-        }
+        i8_issue_k(a, b, h, first, stage_u32, bar_k);
+        i8_issue_v(a, b, h, first, stage_u32, bar_v);
       }
-#pragma unroll
-      for (int s = 0; s < I8_STAGES; ++s)
-        if (first + s * I8_WARPS < p1) inflight |= 1u << ((seq + s) % I8_STAGES);
+      inflight = 3u;
     }
     __syncthreads();   // staged query visible
 
@@ -206,11 +215,11 @@ __global__ void __launch_bounds__(I8_WARPS * 32) decode_paged_i8_kernel(DecodeAr
     float m_run = -INFINITY;
 
     for (int pg = first; pg < p1 && !dead; pg += I8_WARPS) {
-      const uint32_t st = seq % I8_STAGES, parity = (seq / I8_STAGES) & 1u;
-      const uint32_t bar = smem_u32(&ws.bar[st]);
-      if (!mbar_wait(bar, parity)) { dead = true; break; }
-      inflight &= ~(1u << st);
-      const uint8_t *stg = ws.stage[st];
+      const uint32_t parity = seq & 1u;
+      const int nxt = pg + I8_WARPS;
+      if (!mbar_wait(bar_k, parity)) { dead = true; break; }
+      inflight &= ~1u;
+      const uint8_t *stg = ws.stage;
       const uint32_t *kw = reinterpret_cast<const uint32_t *>(stg + I8_OFF_KREC);
       const uint32_t *hw = reinterpret_cast<const uint32_t *>(stg + I8_OFF_KREC + K_OFF_HI);
       const uint32_t *km = reinterpret_cast<const uint32_t *>(stg + I8_OFF_KMETA);
@@ -278,6 +287,11 @@ __global__ void __launch_bounds__(I8_WARPS * 32) decode_paged_i8_kernel(DecodeAr
         const uint32_t b1 = pack_limb(yb[0], yb[1], yb[2], yb[3], limb_sel);
         kstep32<true>(hw, gid, 4 * tig, 16 + 4 * tig, 1, b0, b1, cl);
       }
+      __syncwarp();      // every lane is done with the key part: request the next page's
+      if (nxt < p1) {
+        if (lane == 0) i8_issue_k(a, b, h, nxt, stage_u32, bar_k);
+        inflight |= 1u;
+      }
       // sum_c q*min for head tig: this lane covers arranged positions 16*gid .. 16*gid+15
       float bias = 0.f;
       {
@@ -297,6 +311,8 @@ __global__ void __launch_bounds__(I8_WARPS * 32) decode_paged_i8_kernel(DecodeAr
       }
 
       // ---- value pre-pass (plain token order): scale' = scale * VFIX / max scale, zero-point ---- //
+      if (!mbar_wait(bar_v, parity)) { dead = true; break; }
+      inflight &= ~2u;
       float v_unit;
       {
         float sc[4], zp[4], smax = 0.f;
@@ -373,10 +389,10 @@ __global__ void __launch_bounds__(I8_WARPS * 32) decode_paged_i8_kernel(DecodeAr
           wlo[tg] = __byte_perm(pab, pcd, 0x5410);
           whi[tg] = __byte_perm(pab, pcd, 0x7632);
         }
-        // pb word index = (head*2 + limb)*32 + ks*8 + quad*4 + tg, tokens 16*gid.. <-> ks = gid >> 1, quad = gid & 1
-        uint32_t *dst = ws.pb + (2 * tig) * 32 + (gid >> 1) * 8 + (gid & 1) * 4;
+        // pb word index = (head*2 + limb)*PB_RS + ks*8 + quad*4 + tg, tokens 16*gid.. <-> ks = gid >> 1, quad = gid & 1
+        uint32_t *dst = ws.pb + (2 * tig) * PB_RS + (gid >> 1) * 8 + (gid & 1) * 4;
         *reinterpret_cast<uint4 *>(dst) = make_uint4(whi[0], whi[1], whi[2], whi[3]);
-        *reinterpret_cast<uint4 *>(dst + 32) = make_uint4(wlo[0], wlo[1], wlo[2], wlo[3]);
+        *reinterpret_cast<uint4 *>(dst + PB_RS) = make_uint4(wlo[0], wlo[1], wlo[2], wlo[3]);
       }
       __syncwarp();
 
@@ -387,7 +403,7 @@ __global__ void __launch_bounds__(I8_WARPS * 32) decode_paged_i8_kernel(DecodeAr
       for (int m = 0; m < 8; ++m) cv[m][0] = cv[m][1] = cv[m][2] = cv[m][3] = 0;
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks) {
-        const uint32_t b0 = ws.pb[gid * 32 + ks * 8 + tig], b1 = ws.pb[gid * 32 + ks * 8 + 4 + tig];
+        const uint32_t b0 = ws.pb[gid * PB_RS + ks * 8 + tig], b1 = ws.pb[gid * PB_RS + ks * 8 + 4 + tig];
         kstep32<false>(vw, gid, 32 * ks + tig, 32 * ks + 16 + tig, 4, b0, b1, cv);
       }
       {
@@ -402,33 +418,20 @@ __global__ void __launch_bounds__(I8_WARPS * 32) decode_paged_i8_kernel(DecodeAr
             acc[m][1] = fmaf(static_cast<float>(cv[m][2] * 256 + cv[m][3]), u, acc[m][1]);
           }
       }
-      __syncwarp();      // every lane is done with this stage and with the warp's buffers
+      __syncwarp();      // every lane is done with the value part and with the warp's buffers
       ++seq;
-      const int nxt = pg + I8_STAGES * I8_WARPS;
       if (nxt < p1) {
-        if (lane == 0) {
-          const uint32_t dst = smem_u32(&ws.stage[st][0]);
-          const int64_t pk = a.L.PageTable_K[static_cast<int64_t>(b) * a.L.max_page + nxt];
-          const int64_t pv = a.L.PageTable_V[static_cast<int64_t>(b) * a.L.max_page + nxt];
-          mbar_expect_tx(bar, I8_STAGE_BYTES);
-          bulk_g2s(dst + I8_OFF_KREC, a.L.KeyCache + pk * (static_cast<int64_t>(H) * K_HEAD) + static_cast<int64_t>(h) * K_HEAD, K_HEAD, bar);
-          bulk_g2s(dst + I8_OFF_KMETA, static_cast<const uint8_t *>(a.L.KeyCache_metadata) + (pk * H + h) * META_HEAD, META_HEAD, bar);
-          bulk_g2s(dst + I8_OFF_VREC, a.L.ValueCache + pv * (static_cast<int64_t>(H) * V_HEAD) + static_cast<int64_t>(h) * V_HEAD, V_HEAD, bar);
-          bulk_g2s(dst + I8_OFF_VMETA, static_cast<const uint8_t *>(a.L.ValueCache_metadata) + (pv * H + h) * META_HEAD, META_HEAD, bar);
-        }
-        inflight |= 1u << st;
+        if (lane == 0) i8_issue_v(a, b, h, nxt, stage_u32, bar_v);
+        inflight |= 2u;
       }
     }
 
     if (dead) {
       if (lane == 0) atomicExch(a.status, 1);
-      // give copies still in flight a bounded time to land before the stages are reused or the block exits
-      for (int s = 0; s < I8_STAGES; ++s)
-        if (inflight & (1u << s)) {
-          const uint32_t nseq = seq + ((s + I8_STAGES - seq % I8_STAGES) % I8_STAGES);
-          mbar_wait(smem_u32(&ws.bar[s]), (nseq / I8_STAGES) & 1u);
-          inflight &= ~(1u << s);
-        }
+      // give copies still in flight a bounded time to land before the stage is reused or the block exits
+      if (inflight & 1u) mbar_wait(bar_k, seq & 1u);
+      if (inflight & 2u) mbar_wait(bar_v, seq & 1u);
+      inflight = 0;
     }
     // sum p*zero and sum p over all tokens of the warp's pages: add the 8 row groups
 #pragma unroll
@@ -436,10 +439,10 @@ __global__ void __launch_bounds__(I8_WARPS * 32) decode_paged_i8_kernel(DecodeAr
       zsum += __shfl_xor_sync(0xffffffffu, zsum, o);
       lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
     }
-    __syncthreads();     // all warps have consumed every copy they issued: warp 0's stages can be overlaid
+    __syncthreads();     // all warps have consumed every copy they issued: warp 0's stage can be overlaid
 
     // ---- warp result -> merge buffer [warp][head][PART] ---- //
-    float *mb = reinterpret_cast<float *>(&sm.w[0].stage[0][0]);
+    float *mb = reinterpret_cast<float *>(&sm.w[0].stage[0]);
     {
       float *w = mb + (warp * 4 + tig) * PART;
 #pragma unroll
