@@ -30,7 +30,8 @@ typedef enum {
   KITTY_E_BADSHAPE = -2,  /* geometry other than page 128 / D 128 / 32 boosted / G > 16 */
   KITTY_E_WORKSPACE = -3, /* caller's workspace too small                               */
   KITTY_E_CUDA = -4,      /* a CUDA runtime call failed (see cudaGetLastError)          */
-  KITTY_E_TIMEOUT = -5    /* a bounded device-side wait ran out                         */
+  KITTY_E_TIMEOUT = -5,   /* a bounded device-side wait ran out                         */
+  KITTY_E_STATIC_LIMIT = -6 /* problem needs more scratch than kitty_decode_attn_static has */
 } kitty_status;
 
 typedef enum { KITTY_F16 = 0, KITTY_BF16 = 1, KITTY_F32 = 2 } kitty_dtype;
@@ -156,6 +157,39 @@ int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *counts, cons
                       int32_t B, int32_t h_q, float scaling, void *out, int out_dtype, void *workspace,
                       int64_t workspace_bytes, int32_t page_begin, int32_t page_end, int32_t flags,
                       float *partial_out, int impl, void *stream);
+
+/* Size in bytes of the scratch array built into the library for kitty_decode_attn_static. */
+#define KITTY_STATIC_SCRATCH_BYTES (8u << 20)
+
+/* kitty_decode_attn for callers that must not allocate device memory and have no
+ * buffer to lend as a workspace.  (No counterpart in the reference: its decode
+ * path allocates its scratch tensors inside every call.)
+ *
+ * Who needs it: a host that has handed all free device memory to another
+ * allocator (a framework's caching pool, a serving engine's KV arena), so that a
+ * raw cudaMalloc would fail or fragment that pool; code on a latency-critical
+ * path, where cudaMalloc/cudaFree take a driver-wide lock and may synchronise the
+ * device; and embedders that are only allowed to pass through the tensors they
+ * were given.  For them the split-KV partial results live in a fixed
+ * `static __device__` array of KITTY_STATIC_SCRATCH_BYTES inside the library;
+ * every GPU that loads the library carries that array until the process exits.
+ *
+ * Arguments are those of kitty_decode_attn without workspace/workspace_bytes,
+ * plus status_out: a DEVICE pointer to an int32 (or null) that receives the
+ * bounded-wait status word of this call (0 = fine) when the call's work on the
+ * stream completes.  The entry point calls no cudaMalloc/cudaFree and no
+ * allocating library routine.  The first call on a device looks the array's
+ * address up (cudaGetSymbolAddress, with that device current) and opts the
+ * kernels into large shared memory; make that first call outside any stream
+ * capture.  A problem whose partials do not fit returns KITTY_E_STATIC_LIMIT
+ * before any kernel is launched.  All calls on a device share the one array: the status
+ * word is cleared at the start of each call, everything else is overwritten
+ * before it is read, and two calls that overlap on the GPU (different streams)
+ * race — serialise them. */
+int kitty_decode_attn_static(const kitty_layer *layer, const kitty_counts *counts, const void *query, int q_dtype,
+                             int32_t B, int32_t h_q, float scaling, void *out, int out_dtype, int32_t page_begin,
+                             int32_t page_end, int32_t flags, float *partial_out, int impl, int32_t *status_out,
+                             void *stream);
 
 /* Log-sum-exp combination of n_parts partial results (fp32 [n_parts, rows, 130],
  * the layout partial_out uses; rows = B*h_q) into out [rows, 128] of out_dtype.

@@ -12,6 +12,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "lib", "libkitty_b200.so")
 
 KITTY_OK, KITTY_E_BADARG, KITTY_E_BADSHAPE, KITTY_E_WORKSPACE, KITTY_E_CUDA, KITTY_E_TIMEOUT = 0, -1, -2, -3, -4, -5
+KITTY_E_STATIC_LIMIT = -6
+STATIC_SCRATCH_BYTES = 8 << 20
 KITTY_F16, KITTY_BF16, KITTY_F32 = 0, 1, 2
 SELECT_FUSED, SELECT_SUPPLIED = 0, 1
 DIV_IEEE, DIV_FULL = 0, 1
@@ -19,7 +21,7 @@ DIV_IEEE, DIV_FULL = 0, 1
 EXPORTS = [
     "kitty_version", "kitty_strerror", "kitty_quant_pack_k", "kitty_quant_pack_v", "kitty_prefill_tails",
     "kitty_append", "kitty_flush", "kitty_decode_workspace_bytes", "kitty_workspace_status", "kitty_decode_attn",
-    "kitty_lse_merge",
+    "kitty_lse_merge", "kitty_decode_attn_static",
 ]
 
 
@@ -84,6 +86,9 @@ def lib() -> C.CDLL:
     L.kitty_decode_attn.restype = C.c_int
     L.kitty_decode_attn.argtypes = [C.POINTER(KittyLayer), C.POINTER(KittyCounts), vp, C.c_int, i32, i32, C.c_float,
                                     vp, C.c_int, vp, i64, i32, i32, i32, vp, C.c_int, vp]
+    L.kitty_decode_attn_static.restype = C.c_int
+    L.kitty_decode_attn_static.argtypes = [C.POINTER(KittyLayer), C.POINTER(KittyCounts), vp, C.c_int, i32, i32,
+                                           C.c_float, vp, C.c_int, i32, i32, i32, vp, C.c_int, vp, vp]
     L.kitty_lse_merge.restype = C.c_int
     L.kitty_lse_merge.argtypes = [vp, i32, i64, vp, C.c_int, vp]
     _lib = L

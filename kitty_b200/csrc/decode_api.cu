@@ -200,6 +200,58 @@ extern "C" const char *kitty_strerror(int status) {
     case KITTY_E_WORKSPACE: return "workspace too small (see kitty_decode_workspace_bytes)";
     case KITTY_E_CUDA: return "CUDA runtime error";
     case KITTY_E_TIMEOUT: return "a bounded device-side wait ran out";
+    case KITTY_E_STATIC_LIMIT:
+      return "the problem needs more scratch than the built-in array of kitty_decode_attn_static "
+             "(KITTY_STATIC_SCRATCH_BYTES); use kitty_decode_attn with a caller-owned workspace";
     default: return "unknown status";
   }
+}
+
+// ------------------------------------------------------------------------- //
+// Decode attention without any caller-provided or allocated scratch.
+// ------------------------------------------------------------------------- //
+// The split-KV partials of kitty_decode_attn_static live here.  In host code the
+// name `g_static_scratch` is only a handle for the runtime's symbol table, not a
+// device address: the address is looked up per device below and that pointer is
+// what the kernels receive.
+static __device__ __align__(256) unsigned char g_static_scratch[KITTY_STATIC_SCRATCH_BYTES];
+
+static void *static_scratch_ptr(int *rc) {
+  static void *cached[64] = {nullptr};
+  int dev = 0;
+  *rc = KITTY_OK;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    *rc = KITTY_E_CUDA;
+    return nullptr;
+  }
+  if (cached[dev] == nullptr) {
+    void *p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) {
+      *rc = KITTY_E_CUDA;
+      return nullptr;
+    }
+    cached[dev] = p;
+  }
+  return cached[dev];
+}
+
+extern "C" int kitty_decode_attn_static(const kitty_layer *layer, const kitty_counts *counts, const void *query,
+                                        int q_dtype, int32_t B, int32_t h_q, float scaling, void *out, int out_dtype,
+                                        int32_t page_begin, int32_t page_end, int32_t flags, float *partial_out,
+                                        int impl, int32_t *status_out, void *stream) {
+  int rc = KITTY_OK;
+  void *ws = static_scratch_ptr(&rc);
+  if (rc != KITTY_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // the status word is the one thing that has to start at zero; the partial slots are written before they are read
+  if (cudaMemsetAsync(ws, 0, sizeof(int32_t), s) != cudaSuccess) return KITTY_E_CUDA;
+  rc = kitty_decode_attn(layer, counts, query, q_dtype, B, h_q, scaling, out, out_dtype, ws,
+                         static_cast<int64_t>(KITTY_STATIC_SCRATCH_BYTES), page_begin, page_end, flags, partial_out, impl,
+                         stream);
+  if (rc == KITTY_E_WORKSPACE) return KITTY_E_STATIC_LIMIT;      // checked before anything is launched
+  if (rc != KITTY_OK) return rc;
+  if (status_out != nullptr &&
+      cudaMemcpyAsync(status_out, ws, sizeof(int32_t), cudaMemcpyDeviceToDevice, s) != cudaSuccess)
+    return KITTY_E_CUDA;
+  return KITTY_OK;
 }
