@@ -10,14 +10,14 @@
 //      reads 64 contiguous bytes of a row), packed key pages through the same
 //      code path as the streaming kernel;
 //   2. softmax statistics over the (small) edge, probabilities in place;
-//   3. P.V on the CUDA cores: a warp walks tokens, each lane owns 4 channels
-//      (one 8-byte load per row), then a fixed-order cross-warp reduction;
+//   3. P.V on the CUDA cores: a warp walks tokens (eight rows in flight), each lane
+//      owns 4 channels (one 8-byte load per row), then a fixed-order cross-warp reduction;
 //   4. one partial (acc, max, sum) per query head into the workspace slot.
 #include "paged_core.cuh"
 
 namespace kitty {
 
-constexpr int EDGE_WARPS = 4;
+constexpr int EDGE_WARPS = 8;
 constexpr int EDGE_MAX_TOK = SINK + 3 * PAGE;   // sink + at most two key pages + Q_Buffer_K
 constexpr int S_ROW = EDGE_MAX_TOK + 4;
 
@@ -159,15 +159,16 @@ __global__ void __launch_bounds__(EDGE_WARPS * 32) decode_edge_kernel(DecodeArgs
     if (r < C.Q_Buffer_Count_V) return qbufv + r * HD;
     return ringv + ((r - C.Q_Buffer_Count_V + C.Write_Offset_Local_V) & (PAGE - 1)) * HD;
   };
-  for (int e0 = warp; e0 < ne; e0 += 4 * EDGE_WARPS) {
-    uint2 raw[4];
+  constexpr int UNR = 8;
+  for (int e0 = warp; e0 < ne; e0 += UNR * EDGE_WARPS) {
+    uint2 raw[UNR];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < UNR; ++u) {
       const int e = e0 + u * EDGE_WARPS;
       raw[u] = (e < ne) ? *reinterpret_cast<const uint2 *>(row_of(e)) : make_uint2(0, 0);
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < UNR; ++u) {
       const int e = e0 + u * EDGE_WARPS;
       if (e < ne) {
         const float2 v01 = __half22float2(*reinterpret_cast<const __half2 *>(&raw[u].x));
@@ -201,7 +202,8 @@ __global__ void __launch_bounds__(EDGE_WARPS * 32) decode_edge_kernel(DecodeArgs
 
   // ---- 4. partial result ---- //
   float *dst = a.partials + ((bh * P.n_slots + P.edge_slot) * G) * PART;
-  for (int g = 0; g < G; ++g) dst[g * PART + tid] = sm.red[g][tid];
+  if (tid < HD)
+    for (int g = 0; g < G; ++g) dst[g * PART + tid] = sm.red[g][tid];
   if (tid < G) {
     dst[tid * PART + HD] = (ne > 0) ? sm.mx[tid] : -INFINITY;
     dst[tid * PART + HD + 1] = (ne > 0) ? sm.sum[tid] : 0.f;

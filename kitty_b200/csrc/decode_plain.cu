@@ -186,18 +186,47 @@ __global__ void __launch_bounds__(128) decode_plain_kernel(DecodeArgs a) {
 }
 
 __global__ void __launch_bounds__(128) merge_kernel(MergeArgs a) {
+  // One block per row (batch, query head); thread = channel.  The slot weights are computed
+  // once, in parallel (thread s <-> slot s), then every thread folds its channel over the slots.
+  __shared__ float w_s[128];
+  __shared__ float red[4];
   const int64_t r = blockIdx.x;
-  const int c = threadIdx.x;
+  const int c = threadIdx.x, lane = c & 31, warp = c >> 5;
   const float *base = a.partials + ((r / a.gm) * a.ns * a.gm + r % a.gm) * PART;
-  float M = -INFINITY;
-  for (int s = 0; s < a.n; ++s) M = fmaxf(M, base[s * a.stride_part + HD]);
-  float A = 0.f, Lsum = 0.f;
-  for (int s = 0; s < a.n; ++s) {
-    const float *p = base + s * a.stride_part;
-    const float ms = p[HD];
+  float M = -INFINITY, A = 0.f, Lsum = 0.f;
+  for (int s0 = 0; s0 < a.n; s0 += 128) {           // chunks of 128 slots (one chunk in practice)
+    const int nn = min(128, a.n - s0);
+    const float ms = (c < nn) ? base[(s0 + c) * a.stride_part + HD] : -INFINITY;
+    float mx = ms;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    __syncthreads();                                 // previous chunk's w_s / red are no longer read
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    const float Mn = fmaxf(M, fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3])));
+    const float rescale = (M == -INFINITY) ? 0.f : exp2f(M - Mn);
+    M = Mn;
     const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
-    A = fmaf(p[c], w, A);
-    Lsum = fmaf(p[HD + 1], w, Lsum);
+    w_s[c] = w;
+    float lp = (c < nn) ? base[(s0 + c) * a.stride_part + HD + 1] * w : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) lp += __shfl_xor_sync(0xffffffffu, lp, o);
+    __syncthreads();                                 // red (max) consumed, w_s visible
+    if (lane == 0) red[warp] = lp;
+    __syncthreads();
+    Lsum = Lsum * rescale + ((red[0] + red[1]) + (red[2] + red[3]));
+    A *= rescale;
+    const float *p = base + static_cast<int64_t>(s0) * a.stride_part + c;
+    int s = 0;
+    for (; s + 4 <= nn; s += 4) {
+      const float v0 = p[(s + 0) * a.stride_part], v1 = p[(s + 1) * a.stride_part];
+      const float v2 = p[(s + 2) * a.stride_part], v3 = p[(s + 3) * a.stride_part];
+      A = fmaf(v0, w_s[s], A);
+      A = fmaf(v1, w_s[s + 1], A);
+      A = fmaf(v2, w_s[s + 2], A);
+      A = fmaf(v3, w_s[s + 3], A);
+    }
+    for (; s < nn; ++s) A = fmaf(p[s * a.stride_part], w_s[s], A);
   }
   if (a.partial_out) {
     float *o = a.partial_out + r * PART;
