@@ -31,6 +31,9 @@ sys.path.insert(0, ROOT)
 
 H_KV, H_Q, D, CTX = 8, 32, 128, 32768
 K_PAGE_BYTES, V_PAGE_BYTES = 5760, 4608     # packed record + fp16 metadata per (page, kv-head)
+# dram__bytes_read.sum + dram__bytes_write.sum of decode_paged_i8_kernel divided by the page pairs of the launch,
+# from the ncu capture summarised in profiles/decode_paged_i8_b8_32k_ncu.md (173.14 MB / 16256 pairs)
+DRAM_BYTES_PER_PAGE_PAIR = 10651
 
 
 def parse():
@@ -94,7 +97,7 @@ class ClockSampler:
                         self.reasons.add(n)
             except Exception:
                 pass
-            self._stop.wait(0.05)
+            self._stop.wait(0.004)
 
     def __enter__(self):
         if self.nv is not None:
@@ -346,9 +349,11 @@ def main():
         "gpu_launches": gpu_launches,
         "clocks": clocks.summary(),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_source": peak_src,
-                     "kernel": "decode attention call = decode_paged_kernel + decode_plain_kernel + merge_kernel "
-                               "(algorithmic bytes of the call / CUDA-event time of the call)",
+                     "traffic": B * H_KV * lay.PageCount_V * DRAM_BYTES_PER_PAGE_PAIR, "peak_source": peak_src,
+                     "kernel": "decode attention call = decode_paged_i8_kernel (87.5 % of the step's device time in the "
+                               "ncu launch list) + decode_edge_kernel + merge_kernel; achieved = algorithmic bytes of "
+                               "the call / CUDA-event time of the call; traffic = ncu DRAM bytes of the streaming "
+                               "kernel per page pair (batch-8 capture) x page pairs of one launch",
                      "algorithmic_bytes_per_call": attn_alg / K, "ms_per_call": attn_ms / K},
     }
     if world == 1 and not args.no_cpu_baseline:
