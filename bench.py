@@ -52,6 +52,16 @@ def parse():
 # --------------------------------------------------------------------------- #
 # byte accounting (per sequence = per batch row, all 8 KV heads)
 # --------------------------------------------------------------------------- #
+def partition(ctx: int) -> dict:
+    """How a prompt of ctx tokens is laid out by the cache (sink, packed pages, fp16 tails)."""
+    sink = min(32, ctx)
+    qbuf_k = (ctx - sink) % 128
+    local_v = min(128, ctx - sink)
+    qbuf_v = (ctx - sink - local_v) % 128
+    return dict(sink=sink, qbuf_k=qbuf_k, pages_k=(ctx - sink - qbuf_k) // 128, local_v=local_v, qbuf_v=qbuf_v,
+                pages_v=(ctx - sink - local_v - qbuf_v) // 128)
+
+
 def packed_bytes(pages_k: int, pages_v: int) -> int:
     return H_KV * (pages_k * K_PAGE_BYTES + pages_v * V_PAGE_BYTES)
 
@@ -146,9 +156,7 @@ def cpu_reference(ctx: int, steps: int, warmup: int, budget_s: float = 25.0):
             times.append(dt)
         if s >= warmup + 2 and time.perf_counter() - t_begin > budget_s:
             break
-    from oracle.kitty_oracle import prefill_partition
-
-    p = prefill_partition(ctx)
+    p = partition(ctx)
     per_step = sum(times) / len(times)
     gbs = packed_bytes(p["pages_k"], p["pages_v"]) / per_step / 1e9
     return {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
@@ -166,9 +174,8 @@ def build_cache(kb, batch, ctx, extra, device, seed):
     # the prompt is generated and quantized in slices of 16 sequences to bound transient memory
     lay = cache.kv_cache[0]
     from kitty_b200 import _lib
-    from oracle.kitty_oracle import prefill_partition
 
-    p = prefill_partition(ctx)
+    p = partition(ctx)
     for b0 in range(0, batch, 16):
         b1 = min(batch, b0 + 16)
         k = torch.randn(b1 - b0, H_KV, ctx, D, generator=g, device=device, dtype=torch.float32)

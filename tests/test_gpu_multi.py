@@ -1,0 +1,65 @@
+"""Sequence-split decode on 2 GPUs (NCCL all-gather + kitty_lse_merge) against the
+single-GPU call.  Skipped when fewer than 2 GPUs are visible."""
+import os
+import socket
+import types
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from tests.helpers import make_kv
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, q_out):
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    import kitty_b200 as kb
+    from kitty_b200.seqsplit import seq_split_decode
+
+    h_kv, h_q, B, L = 4, 28, 1, 32 + 40 * 128 + 50          # the long-context shape: 28 query / 4 KV heads
+    cfg = types.SimpleNamespace(num_hidden_layers=1, head_dim=128, num_key_value_heads=h_kv, num_attention_heads=h_q,
+                                hidden_size=128 * h_q)
+    k, v = make_kv(B, h_kv, L, 128, 9, torch.bfloat16)
+    cache = kb.KittyCache(cfg, B, L + 8, device=dev)          # every rank holds the same cache; each reads only its range
+    cache.update(k.to(dev), v.to(dev), 0)
+    cache.quantize_prefill(0)
+    g = torch.Generator().manual_seed(2)
+    cache.update(torch.randn(B, h_kv, 1, 128, generator=g).bfloat16().to(dev),
+                 torch.randn(B, h_kv, 1, 128, generator=g).bfloat16().to(dev), 0)
+    q = torch.randn(B, h_q, 1, 128, generator=g).bfloat16().to(dev)
+    lay = cache.kv_cache[0]
+    full = kb.decode_attention(q, lay, h_kv, 128 ** -0.5)
+    out = seq_split_decode(q, lay, h_kv, 128 ** -0.5, rank=rank, world=world, n_common_pages=lay.PageCount_V)
+    torch.cuda.synchronize(dev)
+    err = (out.float() - full.float()).abs().max().item() / full.float().abs().max().item()
+    q_out.put((rank, err))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(600)
+def test_two_gpu_sequence_split():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=500) for _ in procs]
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert all(e <= 1e-2 for _, e in res), res
