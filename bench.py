@@ -46,6 +46,8 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--sweep", action="store_true", help="also time batch 1/8/32 (attention call only)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "quantize"],
+                    help="decode (the headline metric) or quantize (bulk prefill quantize/pack throughput)")
     return ap.parse_args()
 
 
@@ -200,8 +202,68 @@ def build_cache(kb, batch, ctx, extra, device, seed):
     return cache
 
 
+def quantize_workload(args):
+    """Bulk prefill quantize/pack: 65536 tokens x 8 KV heads x head_dim 128 per layer call, bf16 Gaussian K/V with
+    per-(head, channel) scales log-uniform in [1, 16]; 32 layer calls per step (distinct inputs cycle through 4
+    buffers of 268 MB, larger than L2)."""
+    import kitty_b200 as kb
+
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    T, layers, nbuf = 65536, 32, 4
+    g = torch.Generator(device=device).manual_seed(5)
+    ks, vs = [], []
+    for _ in range(nbuf):
+        sc = torch.exp(torch.rand(1, H_KV, 1, D, generator=g, device=device) * 2.772588722239781)
+        ks.append((torch.randn(1, H_KV, T, D, generator=g, device=device) * sc).to(torch.bfloat16))
+        vs.append(torch.randn(1, H_KV, T, D, generator=g, device=device).to(torch.bfloat16))
+    pages = T // 128
+    z = dict(device=device)
+    kc = torch.zeros(pages, H_KV * 5248, dtype=torch.uint8, **z)
+    km = torch.zeros(pages, H_KV, 128, 2, dtype=torch.float16, **z)
+    vc = torch.zeros(pages, H_KV * 4096, dtype=torch.uint8, **z)
+    vm = torch.zeros(pages, H_KV, 128, 2, dtype=torch.float16, **z)
+    pt = torch.arange(pages, dtype=torch.int64, **z).view(1, pages)
+
+    def step():
+        for l in range(layers):
+            kb.quantize_pack_k(ks[l % nbuf], 0, pages, pt, 0, kc, km, 128, 32)
+            kb.quantize_pack_v(vs[l % nbuf], 0, pages, pt, 0, vc, vm, 128)
+
+    W, K = max(3, args.warmup), args.steps
+    for _ in range(W):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ek = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    e0.record()
+    for i in range(K):
+        step()
+        ek[i][0].record()
+        kb.quantize_pack_k(ks[0], 0, pages, pt, 0, kc, km, 128, 32)       # one extra K call timed alone
+        ek[i][1].record()
+    e1.record()
+    torch.cuda.synchronize()
+    k_ms = sum(a.elapsed_time(b) for a, b in ek) / K
+    ms = (e0.elapsed_time(e1) - k_ms * K) / K
+    units = layers * pages * H_KV
+    alg = units * (38528 + 37376)
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peak = json.load(open(peaks_path))["hbm_gbs"] if os.path.exists(peaks_path) else 6650.0
+    k_gbs = pages * H_KV * 38528 / (k_ms * 1e-3) / 1e9
+    print(json.dumps({"metric": "prefill_quantize_pack_throughput", "value": alg / (ms * 1e-3) / 1e9, "unit": "GB/s",
+                      "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms, "higher_is_better": True,
+                      "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": "65536 tokens x 32 layers x 8 KV heads x head_dim 128, bf16, K and V"},
+                      "roofline": {"bound": "hbm", "achieved": alg / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                                   "frac": alg / (ms * 1e-3) / 1e9 / peak, "traffic": None,
+                                   "pack_k_kernel_GBps": k_gbs, "pack_k_kernel_frac": k_gbs / peak}}))
+
+
 def main():
     args = parse()
+    if args.workload == "quantize" and args.impl == "ours":
+        return quantize_workload(args)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -1,0 +1,86 @@
+"""The attention patch for stock HuggingFace models: wiring on CPU (fake cache),
+end to end on a GPU (tiny random Llama)."""
+import pytest
+import torch
+
+
+def _tiny(dtype=torch.float32):
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    torch.manual_seed(0)
+    cfg = LlamaConfig(hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=128, vocab_size=1000, max_position_embeddings=4096)
+    return cfg, LlamaForCausalLM(cfg).eval().to(dtype)
+
+
+class _PrefillOnlyCache:
+    def __init__(self):
+        self.quantized = []
+
+    def update(self, k, v, i):
+        assert k.shape[1] == 2 and k.shape[-1] == 128
+        return True
+
+    def quantize_prefill(self, i):
+        self.quantized.append(i)
+
+    def get_seq_length(self, i=0):
+        return 0
+
+
+def test_patched_prefill_equals_stock_model_on_cpu():
+    from kitty_b200.hf_adapter import patch_model
+
+    cfg, m = _tiny()
+    _, stock = _tiny()
+    stock.load_state_dict(m.state_dict())
+    assert patch_model(m) == 2
+    ids = torch.randint(0, 1000, (2, 24))
+    c = _PrefillOnlyCache()
+    with torch.no_grad():
+        a = m.model(input_ids=ids, position_ids=torch.arange(24).unsqueeze(0), past_key_values=c, use_cache=True).last_hidden_state
+        b = stock.model(input_ids=ids).last_hidden_state
+    assert c.quantized == [0, 1]
+    assert torch.allclose(a, b, atol=1e-5)
+
+
+@pytest.mark.gpu
+def test_greedy_decode_matches_stock_model_while_nothing_is_quantized():
+    """Prompt of 100 tokens + 20 steps stays inside sink + Q-buffer + ring (all fp16): the patched model with the
+    Kitty cache must follow the stock model with HF's own cache."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import kitty_b200 as kb
+    from kitty_b200.hf_adapter import greedy_decode, patch_model
+
+    cfg, m = _tiny(torch.float16)
+    _, stock = _tiny(torch.float16)
+    stock.load_state_dict(m.state_dict())
+    m, stock = m.cuda(), stock.cuda()
+    patch_model(m)
+    ids = torch.randint(0, 1000, (3, 100), device="cuda")
+    cache = kb.get_kvcache_kitty(cfg, 3, 512, device="cuda:0")
+    got = greedy_decode(m, ids, 20, cache)
+    want = stock.generate(ids, max_new_tokens=20, do_sample=False, eos_token_id=None, pad_token_id=0)[:, 100:]
+    assert cache.get_seq_length(0) == 119
+    agree = (got == want).float().mean().item()
+    assert agree >= 0.9, agree        # random-init logits are nearly flat: allow a few fp16 near-ties
+
+
+@pytest.mark.gpu
+def test_greedy_decode_long_prompt_runs_through_flushes():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import kitty_b200 as kb
+    from kitty_b200.hf_adapter import greedy_decode, patch_model
+
+    cfg, m = _tiny(torch.bfloat16)
+    m = m.cuda()
+    patch_model(m)
+    ids = torch.randint(0, 1000, (2, 700), device="cuda")
+    cache = kb.get_kvcache_kitty(cfg, 2, 1024, device="cuda:0")
+    out = greedy_decode(m, ids, 140, cache)
+    assert out.shape == (2, 140) and int(out.min()) >= 0
+    lay = cache.kv_cache[1]
+    assert cache.get_seq_length(1) == 700 + 139
+    assert lay.PageCount_K == (700 + 139 - 32) // 128 and lay.PageCount_V == lay.PageCount_K - 1
