@@ -27,6 +27,9 @@ class _PrefillOnlyCache:
     def get_seq_length(self, i=0):
         return 0
 
+    def get_mask_sizes(self, cache_position, i=0):
+        return (cache_position.shape[0] if hasattr(cache_position, "shape") else int(cache_position)), 0
+
 
 def test_patched_prefill_equals_stock_model_on_cpu():
     from kitty_b200.hf_adapter import patch_model
