@@ -46,8 +46,10 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--sweep", action="store_true", help="also time batch 1/8/32 (attention call only)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "quantize"],
-                    help="decode (the headline metric) or quantize (bulk prefill quantize/pack throughput)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "quantize", "e2e"],
+                    help="decode (the headline metric), quantize (bulk prefill quantize/pack throughput) or e2e "
+                         "(Llama-3-8B-shaped random-init decoder: batch 16, 4096-token prompts, 256 greedy steps)")
+    ap.add_argument("--layers", type=int, default=32, help="decoder layers of the e2e workload")
     return ap.parse_args()
 
 
@@ -260,10 +262,67 @@ def quantize_workload(args):
                                    "pack_k_kernel_GBps": k_gbs, "pack_k_kernel_frac": k_gbs / peak}}))
 
 
+def e2e_workload(args):
+    """Random-init Llama-3-8B-shaped decoder (hidden 4096, 32q/8kv heads, head_dim 128, inter 14336, vocab 128256),
+    bf16, batch 16, prompts of 4096 uniform-random token ids (seed 0), 256 greedy decode steps with a fresh
+    KittyCache — the method of the reference's latency benchmark (fresh cache, greedy, fixed length)."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    import kitty_b200 as kb
+    from kitty_b200.hf_adapter import greedy_decode, patch_model
+
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    B, L, steps = 16, 4096, 256
+    cfg = LlamaConfig(hidden_size=4096, intermediate_size=14336, num_hidden_layers=args.layers, num_attention_heads=32,
+                      num_key_value_heads=8, head_dim=128, vocab_size=128256, max_position_embeddings=8192,
+                      rope_theta=500000.0, tie_word_embeddings=False)
+    torch.manual_seed(0)
+    old = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    with torch.device(device):
+        model = LlamaForCausalLM(cfg).eval()
+    torch.set_default_dtype(old)
+    patch_model(model)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, 128256, (B, L), generator=g).to(device)
+
+    def run():
+        cache = kb.get_kvcache_kitty(cfg, B, L + steps + 8, device=device)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        with torch.no_grad():
+            pos = torch.arange(L, device=device).unsqueeze(0)
+            hs = model.model(input_ids=ids, position_ids=pos, past_key_values=cache, use_cache=True).last_hidden_state
+            tok = model.lm_head(hs[:, -1:, :]).argmax(-1)
+            torch.cuda.synchronize()
+            t1 = time.perf_counter()
+            for s_ in range(1, steps):
+                p = torch.full((1, 1), L + s_ - 1, device=device, dtype=torch.long)
+                hs = model.model(input_ids=tok, position_ids=p, past_key_values=cache, use_cache=True).last_hidden_state
+                tok = model.lm_head(hs).argmax(-1)
+            torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        del cache
+        return t1 - t0, t2 - t1
+
+    run()                                   # warm-up generate (fresh cache per run, as the reference benchmark does)
+    pre, dec = zip(*[run() for _ in range(max(1, min(args.steps, 3)))])
+    dec_s, pre_s = min(dec), min(pre)
+    print(json.dumps({"metric": "e2e_decode_tokens_per_s", "value": B * (steps - 1) / dec_s, "unit": "tokens/s",
+                      "n_gpus": 1, "steps": steps, "ms_per_step": dec_s / (steps - 1) * 1e3, "higher_is_better": True,
+                      "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": f"random-init Llama-3-8B shape, {args.layers} layers, batch 16, prompt 4096, "
+                                             "256 greedy steps, KittyCache", "prefill_s": pre_s, "decode_s": dec_s,
+                                 "generate_s": pre_s + dec_s}}))
+
+
 def main():
     args = parse()
     if args.workload == "quantize" and args.impl == "ours":
         return quantize_workload(args)
+    if args.workload == "e2e" and args.impl == "ours":
+        return e2e_workload(args)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
