@@ -46,7 +46,7 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--sweep", action="store_true", help="also time batch 1/8/32 (attention call only)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "quantize", "e2e"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "quantize", "e2e", "seqsplit"],
                     help="decode (the headline metric), quantize (bulk prefill quantize/pack throughput) or e2e "
                          "(Llama-3-8B-shaped random-init decoder: batch 16, 4096-token prompts, 256 greedy steps)")
     ap.add_argument("--layers", type=int, default=32, help="decoder layers of the e2e workload")
@@ -317,8 +317,74 @@ def e2e_workload(args):
                                  "generate_s": pre_s + dec_s}}))
 
 
+def seqsplit_workload(args):
+    """Long-context layer step: 28 query / 4 KV heads, batch 1, 131072 cached tokens, the 1022 common pages split in
+    contiguous ranges over the ranks (sink on rank 0, tail on the last rank); per step every rank reduces its range,
+    the [28, 130] fp32 partials are all-gathered over NCCL and merged.  Launch under torchrun for N > 1."""
+    global H_KV, H_Q
+    import kitty_b200 as kb
+    from kitty_b200.seqsplit import seq_split_decode
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+    H_KV, H_Q = 4, 28
+    ctx = 131072
+    W, K = max(3, args.warmup), args.steps
+    cache = build_cache(kb, 1, ctx, W + K, device, seed=4321)      # same seed: every rank holds the same sequence
+    lay = cache.kv_cache[0]
+    g = torch.Generator(device=device).manual_seed(17)
+    qs = torch.randn(W + K, 1, H_Q, 1, D, generator=g, device=device).to(torch.bfloat16)
+    ks = torch.randn(W + K, 1, H_KV, 1, D, generator=g, device=device).to(torch.bfloat16)
+    vs = torch.randn(W + K, 1, H_KV, 1, D, generator=g, device=device).to(torch.bfloat16)
+
+    def step(i):
+        cache.update(ks[i], vs[i], 0)
+        out = seq_split_decode(qs[i], lay, H_KV, D ** -0.5, rank=rank, world=world, n_common_pages=lay.PageCount_V)
+        cache.quantize_decode(0)
+        return out
+
+    for i in range(W):
+        step(i)
+    torch.cuda.synchronize(device)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    tot = 0.0
+    for i in range(K):
+        flush.zero_()                         # evict the cache from L2: one rank's share (5-43 MB) would otherwise stay resident
+        e0.record()
+        step(W + i)
+        e1.record()
+        e1.synchronize()
+        tot += e0.elapsed_time(e1)
+    t = torch.tensor([tot], device=device, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t[0]) / K
+    if rank == 0:
+        packed = H_KV * (lay.PageCount_K * K_PAGE_BYTES + lay.PageCount_V * V_PAGE_BYTES)
+        print(json.dumps({"metric": "seqsplit_layer_step_latency", "value": ms * 1e3, "unit": "us", "n_gpus": world,
+                          "steps": K, "warmup": W, "higher_is_better": False, "dtype": "f16", "data": "synthetic",
+                          "packed_kv_GBps_aggregate": packed / (ms * 1e-3) / 1e9,
+                          "config": {"workload": "1 layer, 28q/4kv heads, batch 1, 131072 cached tokens, sequence split "
+                                                 f"over {world} GPU(s), L2 flushed between steps",
+                                     "collective": "all_gather of [28,130] fp32 per rank + merge"}}))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     args = parse()
+    if args.workload == "seqsplit" and args.impl == "ours":
+        return seqsplit_workload(args)
     if args.workload == "quantize" and args.impl == "ours":
         return quantize_workload(args)
     if args.workload == "e2e" and args.impl == "ours":
@@ -375,7 +441,7 @@ def main():
         out, _ = kb.kitty_attention_forward(mod, q, lay, scaling)
         flush = lay.Q_Buffer_Count_K == 128 or lay.Q_Buffer_Count_V == 128
         cache.quantize_decode(0)
-        launches["n"] += 4 + (1 if flush else 0)      # append, streaming, plain, merge (+ flush)
+        launches["n"] += 3 + (1 if flush else 0)      # append, streaming (pages + edges), merge (+ flush)
         return out
 
     def barrier():
@@ -404,7 +470,7 @@ def main():
             attn_ev[i][1].record()
             flush = lay.Q_Buffer_Count_K == 128 or lay.Q_Buffer_Count_V == 128
             cache.quantize_decode(0)
-            launches["n"] += 4 + (1 if flush else 0)
+            launches["n"] += 3 + (1 if flush else 0)
         ev1.record()
         barrier()
     ms = ev0.elapsed_time(ev1)
@@ -478,8 +544,8 @@ def main():
         "clocks": clocks.summary(),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": B * H_KV * lay.PageCount_V * DRAM_BYTES_PER_PAGE_PAIR, "peak_source": peak_src,
-                     "kernel": "decode attention call = decode_paged_i8_kernel (87.5 % of the step's device time in the "
-                               "ncu launch list) + decode_edge_kernel + merge_kernel; achieved = algorithmic bytes of "
+                     "kernel": "decode attention call = decode_paged_i8_kernel (page pairs and edges, >97 % of the "
+                               "step's device time in the ncu launch list) + merge_kernel; achieved = algorithmic bytes of "
                                "the call / CUDA-event time of the call; traffic = ncu DRAM bytes of the streaming "
                                "kernel per page pair (batch-8 capture) x page pairs of one launch",
                      "algorithmic_bytes_per_call": attn_alg / K, "ms_per_call": attn_ms / K},

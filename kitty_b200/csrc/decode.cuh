@@ -56,7 +56,7 @@ struct MergeArgs {
 
 int launch_decode_plain(const DecodeArgs &a, int items_per_bh, cudaStream_t s);
 int launch_decode_paged(const DecodeArgs &a, int n_items, int n_gt, int grid, cudaStream_t s);
-int launch_decode_paged_i8(const DecodeArgs &a, int n_items, int grid, cudaStream_t s);
+int launch_decode_paged_i8(const DecodeArgs &a, int n_items, int n_edge, int grid, cudaStream_t s);
 int launch_decode_edge(const DecodeArgs &a, cudaStream_t s);
 int launch_merge(const MergeArgs &m, cudaStream_t s);
 

@@ -134,16 +134,20 @@ extern "C" int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *c
   a.partials = reinterpret_cast<float *>(static_cast<uint8_t *>(workspace) + WS_HEADER);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
-  if (P.fast_chunks && P.nchunk > 0) {
-    const int64_t items = static_cast<int64_t>(B) * H * n_gt * P.nchunk;
-    const int grid = static_cast<int>(std::min<int64_t>(items, grid_max));
-    if (use_i8) {
-      if (int rc = launch_decode_paged_i8(a, static_cast<int>(items), grid, s)) return rc;
-    } else {
+  if (use_i8) {
+    // the int8 streaming kernel also reduces the edge (sink + tail) inside its own grid
+    const int64_t items = static_cast<int64_t>(B) * H * P.nchunk;
+    const int64_t n_edge = has_edge ? static_cast<int64_t>(B) * H : 0;
+    if (items + n_edge > 0) {
+      const int grid = static_cast<int>(std::min<int64_t>(items + n_edge, grid_max));
+      if (int rc = launch_decode_paged_i8(a, static_cast<int>(items), static_cast<int>(n_edge), grid, s)) return rc;
+    }
+  } else if (P.fast_chunks) {
+    if (P.nchunk > 0) {
+      const int64_t items = static_cast<int64_t>(B) * H * n_gt * P.nchunk;
+      const int grid = static_cast<int>(std::min<int64_t>(items, grid_max));
       if (int rc = launch_decode_paged(a, static_cast<int>(items), n_gt, grid, s)) return rc;
     }
-  }
-  if (P.fast_chunks) {
     if (has_edge)
       if (int rc = launch_decode_edge(a, s)) return rc;
   } else {

@@ -1,220 +1,23 @@
-// Edge kernel: the part of a decode-attention call that is not a pair of packed
-// pages — the fp16 sink tokens and the tail of the sequence (key pages that have
-// no packed value page yet, Q_Buffer_K, Q_Buffer_V, the rotated value ring;
-// kernels/kitty_attention.py:88-113, 183-207, 269-289, 336-386 of the reference).
-// At most 32 + 384 tokens per (batch, kv-head), ~100 KB of fp16 rows.
-//
-// One block per (batch, kv-head):
-//   1. logits of every edge token into shared memory — fp16 key rows go through
-//      mma.sync with A fragments loaded straight from global memory (each lane
-//      reads 64 contiguous bytes of a row), packed key pages through the same
-//      code path as the streaming kernel;
-//   2. softmax statistics over the (small) edge, probabilities in place;
-//   3. P.V on the CUDA cores: a warp walks tokens (eight rows in flight), each lane
-//      owns 4 channels (one 8-byte load per row), then a fixed-order cross-warp reduction;
-//   4. one partial (acc, max, sum) per query head into the workspace slot.
-#include "paged_core.cuh"
+// Stand-alone edge kernel: one block of 8 warps per (batch, kv-head).  Used with the fp16 streaming
+// kernel; the int8 streaming kernel runs the same reduction inside its own grid.
+#include "decode_edge.cuh"
 
 namespace kitty {
 
-constexpr int EDGE_WARPS = 8;
-constexpr int EDGE_MAX_TOK = SINK + 3 * PAGE;   // sink + at most two key pages + Q_Buffer_K
-constexpr int S_ROW = EDGE_MAX_TOK + 4;
-
-struct EdgeSmem {
-  float S[MAX_GROUP][S_ROW];                 // logits, then probabilities
-  float red[MAX_GROUP][HD];                  // cross-warp reduction of the output
-  __align__(16) __half qs[MAX_GROUP][QS_ROW];
-  __align__(16) uint8_t krec[2][K_HEAD];
-  __align__(16) uint32_t kmeta[2][HD];
-  float mx[MAX_GROUP], sum[MAX_GROUP];
-  uint8_t inv[EDGE_WARPS][DB];
-};
+constexpr int EDGE_KERNEL_WARPS = 8;
 
 template <int NG>
-__global__ void __launch_bounds__(EDGE_WARPS * 32) decode_edge_kernel(DecodeArgs a) {
+__global__ void __launch_bounds__(EDGE_KERNEL_WARPS * 32) decode_edge_kernel(DecodeArgs a) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  EdgeSmem &sm = *reinterpret_cast<EdgeSmem *>(smem_raw);
-  const DecodePlan &P = a.P;
-  const kitty_counts &C = a.C;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
-  const int h = blockIdx.x, b = blockIdx.y, H = P.H, G = P.G;
-  const int64_t bh = static_cast<int64_t>(b) * H + h;
-  const int n_gt = (G + 7) >> 3;
-
-  const int sink_n = P.has_sink ? C.Sink_Count : 0;
-  const int npk = P.has_tail ? (C.PageCount_K - C.PageCount_V) : 0;     // key pages without a packed value page
-  const int qk_n = P.has_tail ? C.Q_Buffer_Count_K : 0;
-  const int tail_n = npk * PAGE + qk_n;
-  const int ne = sink_n + tail_n;
-
-  // ---- stage the query and the tail's packed key pages ---- //
-  for (int i = tid; i < MAX_GROUP * HD; i += EDGE_WARPS * 32) {
-    const int g = i >> 7, d = i & (HD - 1);
-    float v = 0.f;
-    if (g < G) v = load_q(a.q, a.q_dtype, (static_cast<int64_t>(b) * P.h_q + h * G + g) * HD + d) * a.scale_log2;
-    sm.qs[g][d] = __float2half_rn(v);
-  }
-  if (tid < EDGE_WARPS * DB) sm.inv[tid / DB][tid % DB] = 0;
-  for (int p = 0; p < npk; ++p) {
-    const int64_t pid = a.L.PageTable_K[static_cast<int64_t>(b) * a.L.max_page + C.PageCount_V + p];
-    const uint4 *src = reinterpret_cast<const uint4 *>(a.L.KeyCache + pid * (static_cast<int64_t>(H) * K_HEAD) + h * K_HEAD);
-    for (int i = tid; i < K_HEAD / 16; i += EDGE_WARPS * 32) reinterpret_cast<uint4 *>(sm.krec[p])[i] = src[i];
-    const uint4 *ms = reinterpret_cast<const uint4 *>(static_cast<const uint8_t *>(a.L.KeyCache_metadata) + (pid * H + h) * META_HEAD);
-    if (tid < META_HEAD / 16) reinterpret_cast<uint4 *>(sm.kmeta[p])[tid] = ms[tid];
-  }
-  __syncthreads();
-
-  // ---- 1a. packed key pages of the tail: one (page, group of 8 heads) per warp ---- //
-  if (warp < npk * n_gt) {
-    const int p = warp / n_gt, gt = warp % n_gt;
-    uint32_t q2[8][2];
-    load_q_frags(&sm.qs[gt * 8], gid, tig, q2);
-    float cl[8][4];
-    qk_packed_page(sm.krec[p], sm.kmeta[p], &sm.qs[gt * 8], q2, sm.inv[warp], lane, cl);
-    const int e0 = sink_n + p * PAGE + 16 * gid;
-#pragma unroll
-    for (int m = 0; m < 8; ++m) {
-      sm.S[gt * 8 + 2 * tig][e0 + m] = cl[m][0];
-      sm.S[gt * 8 + 2 * tig + 1][e0 + m] = cl[m][1];
-      sm.S[gt * 8 + 2 * tig][e0 + 8 + m] = cl[m][2];
-      sm.S[gt * 8 + 2 * tig + 1][e0 + 8 + m] = cl[m][3];
-    }
-  }
-  // ---- 1b. fp16 key rows (sink, Q_Buffer_K): 16-token tiles ---- //
-  {
-    const int ns_t = (sink_n + 15) >> 4, nq_t = (qk_n + 15) >> 4;
-    for (int j = warp; j < ns_t + nq_t; j += EDGE_WARPS) {
-      const __half *base;
-      int row0, nrows, e0;
-      if (j < ns_t) {
-        base = static_cast<const __half *>(a.L.Sink_Buffer_K) + bh * SINK * HD;
-        row0 = 16 * j; nrows = sink_n; e0 = row0;
-      } else {
-        base = static_cast<const __half *>(a.L.Q_Buffer_K) + bh * PAGE * HD;
-        row0 = 16 * (j - ns_t); nrows = qk_n; e0 = sink_n + npk * PAGE + row0;
-      }
-      // lane (gid, tig): rows row0+gid and row0+gid+8, channels [32*tig, 32*tig+32)
-      uint4 ra[4], rb[4];
-      const int rA = row0 + gid, rB = row0 + gid + 8;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        ra[i] = (rA < nrows) ? *reinterpret_cast<const uint4 *>(base + rA * HD + 32 * tig + 8 * i) : make_uint4(0, 0, 0, 0);
-        rb[i] = (rB < nrows) ? *reinterpret_cast<const uint4 *>(base + rB * HD + 32 * tig + 8 * i) : make_uint4(0, 0, 0, 0);
-      }
-      const uint32_t *wa = reinterpret_cast<const uint32_t *>(ra), *wb = reinterpret_cast<const uint32_t *>(rb);
-      for (int gt = 0; gt < n_gt; ++gt) {
-        float c[4] = {0.f, 0.f, 0.f, 0.f};
-        // contraction index k = 2*tig, 2*tig+1 <-> channels 32*tig + 4*ks + {0,1}; k = 2*tig+8, +9 <-> + {2,3}
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint2 qq = *reinterpret_cast<const uint2 *>(&sm.qs[gt * 8 + gid][32 * tig + 4 * ks]);
-          mma16816(c, wa[2 * ks], wb[2 * ks], wa[2 * ks + 1], wb[2 * ks + 1], qq.x, qq.y);
-        }
-        const int g0 = gt * 8 + 2 * tig;
-        if (rA < nrows) {
-          sm.S[g0][e0 + gid] = c[0];
-          sm.S[g0 + 1][e0 + gid] = c[1];
-        }
-        if (rB < nrows) {
-          sm.S[g0][e0 + gid + 8] = c[2];
-          sm.S[g0 + 1][e0 + gid + 8] = c[3];
-        }
-      }
-    }
-  }
-  __syncthreads();
-
-  // ---- 2. softmax statistics per query head; probabilities replace the logits ---- //
-  for (int g = warp; g < G; g += EDGE_WARPS) {
-    float mx = -INFINITY;
-    for (int e = lane; e < ne; e += 32) mx = fmaxf(mx, sm.S[g][e]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    float s = 0.f;
-    for (int e = lane; e < ne; e += 32) {
-      const float p = ex2(sm.S[g][e] - mx);
-      sm.S[g][e] = p;
-      s += p;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (lane == 0) {
-      sm.mx[g] = mx;
-      sm.sum[g] = s;
-    }
-  }
-  __syncthreads();
-
-  // ---- 3. P.V: warp walks tokens warp, warp+4, ...; lane owns channels 4*lane..4*lane+3 ---- //
-  float acc[NG][4];
-#pragma unroll
-  for (int g = 0; g < NG; ++g) acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
-  const __half *sinkv = static_cast<const __half *>(a.L.Sink_Buffer_V) + bh * SINK * HD + 4 * lane;
-  const __half *qbufv = static_cast<const __half *>(a.L.Q_Buffer_V) + bh * PAGE * HD + 4 * lane;
-  const __half *ringv = static_cast<const __half *>(a.L.Local_Buffer_V) + bh * PAGE * HD + 4 * lane;
-  auto row_of = [&](int e) -> const __half * {
-    if (e < sink_n) return sinkv + e * HD;
-    const int r = e - sink_n;
-    if (r < C.Q_Buffer_Count_V) return qbufv + r * HD;
-    return ringv + ((r - C.Q_Buffer_Count_V + C.Write_Offset_Local_V) & (PAGE - 1)) * HD;
-  };
-  constexpr int UNR = 8;
-  for (int e0 = warp; e0 < ne; e0 += UNR * EDGE_WARPS) {
-    uint2 raw[UNR];
-#pragma unroll
-    for (int u = 0; u < UNR; ++u) {
-      const int e = e0 + u * EDGE_WARPS;
-      raw[u] = (e < ne) ? *reinterpret_cast<const uint2 *>(row_of(e)) : make_uint2(0, 0);
-    }
-#pragma unroll
-    for (int u = 0; u < UNR; ++u) {
-      const int e = e0 + u * EDGE_WARPS;
-      if (e < ne) {
-        const float2 v01 = __half22float2(*reinterpret_cast<const __half2 *>(&raw[u].x));
-        const float2 v23 = __half22float2(*reinterpret_cast<const __half2 *>(&raw[u].y));
-#pragma unroll
-        for (int g = 0; g < NG; ++g) {
-          const float p = sm.S[g][e];      // rows g >= G hold stale data; their results are never written
-          acc[g][0] = fmaf(p, v01.x, acc[g][0]);
-          acc[g][1] = fmaf(p, v01.y, acc[g][1]);
-          acc[g][2] = fmaf(p, v23.x, acc[g][2]);
-          acc[g][3] = fmaf(p, v23.y, acc[g][3]);
-        }
-      }
-    }
-  }
-  for (int w = 0; w < EDGE_WARPS; ++w) {
-    if (warp == w) {
-#pragma unroll
-      for (int g = 0; g < NG; ++g) {
-        float4 *dst = reinterpret_cast<float4 *>(&sm.red[g][4 * lane]);
-        float4 v = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
-        if (w > 0) {
-          const float4 o = *dst;
-          v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-        }
-        *dst = v;
-      }
-    }
-    __syncthreads();
-  }
-
-  // ---- 4. partial result ---- //
-  float *dst = a.partials + ((bh * P.n_slots + P.edge_slot) * G) * PART;
-  if (tid < HD)
-    for (int g = 0; g < G; ++g) dst[g * PART + tid] = sm.red[g][tid];
-  if (tid < G) {
-    dst[tid * PART + HD] = (ne > 0) ? sm.mx[tid] : -INFINITY;
-    dst[tid * PART + HD + 1] = (ne > 0) ? sm.sum[tid] : 0.f;
-  }
+  EdgeSmem<EDGE_KERNEL_WARPS> &sm = *reinterpret_cast<EdgeSmem<EDGE_KERNEL_WARPS> *>(smem_raw);
+  edge_item<NG, EDGE_KERNEL_WARPS>(a, sm, blockIdx.y, blockIdx.x);
 }
 
 int launch_decode_edge(const DecodeArgs &a, cudaStream_t s) {
   static int configured = -1;     // per-process opt-in to > 48 KB dynamic shared memory, once per device
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return KITTY_E_CUDA;
-  const int smem = static_cast<int>(sizeof(EdgeSmem));
+  const int smem = static_cast<int>(sizeof(EdgeSmem<EDGE_KERNEL_WARPS>));
   if (configured != dev) {
     if (cudaFuncSetAttribute(decode_edge_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
         cudaFuncSetAttribute(decode_edge_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
@@ -223,9 +26,9 @@ int launch_decode_edge(const DecodeArgs &a, cudaStream_t s) {
     configured = dev;
   }
   dim3 grid(a.P.H, a.P.B);
-  if (a.P.G <= 4) decode_edge_kernel<4><<<grid, EDGE_WARPS * 32, smem, s>>>(a);
-  else if (a.P.G <= 8) decode_edge_kernel<8><<<grid, EDGE_WARPS * 32, smem, s>>>(a);
-  else decode_edge_kernel<16><<<grid, EDGE_WARPS * 32, smem, s>>>(a);
+  if (a.P.G <= 4) decode_edge_kernel<4><<<grid, EDGE_KERNEL_WARPS * 32, smem, s>>>(a);
+  else if (a.P.G <= 8) decode_edge_kernel<8><<<grid, EDGE_KERNEL_WARPS * 32, smem, s>>>(a);
+  else decode_edge_kernel<16><<<grid, EDGE_KERNEL_WARPS * 32, smem, s>>>(a);
   return cudaGetLastError() == cudaSuccess ? KITTY_OK : KITTY_E_CUDA;
 }
 

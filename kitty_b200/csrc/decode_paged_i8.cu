@@ -30,7 +30,7 @@
 //
 // Every wait on an mbarrier is bounded; when one runs out the warp sets the
 // workspace's status word, stops consuming and the call's result is invalid.
-#include "paged_core.cuh"
+#include "decode_edge.cuh"
 
 namespace kitty {
 
@@ -59,16 +59,26 @@ struct I8Warp {
   __align__(16) float sarr[HD];        // keys: scale' per channel (arranged); values: scale' per token (plain)
   __align__(16) float marr[HD];        // keys: min per channel (arranged);    values: zero-point per token (plain)
   __align__(16) uint32_t pb[8 * PB_RS]; // probabilities * scale' as limb bytes: [head*2 + limb][k-step][quad][tg] words
-  __align__(8) unsigned long long bar_k, bar_v;
   uint8_t inv[DB];                     // slot -> arranged position of its channel
 };
 
-struct I8Smem {
+struct I8Main {
   I8Warp w[I8_WARPS];
   __align__(16) float qarr[4][QROW];   // query / qmax per head, arranged
   float qmax[4];
 };
+
+// A block alternates between page-pair items and edge items (sink + tail of one (batch, kv-head)); the two
+// kinds reuse the same shared memory.  The mbarriers live outside the shared region.
+struct I8Smem {
+  union {
+    I8Main m;
+    EdgeSmem<I8_WARPS> e;
+  } u;
+  __align__(8) unsigned long long bar_k[I8_WARPS], bar_v[I8_WARPS];
+};
 static_assert(I8_WARPS * 4 * PART * 4 <= I8_STAGE_BYTES, "merge buffer overlays warp 0's stage");
+static_assert(sizeof(I8Smem) <= 56 * 1024, "four blocks per SM");
 
 __device__ __forceinline__ void imma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                           uint32_t b1) {
@@ -141,9 +151,10 @@ __device__ __forceinline__ void i8_issue_v(const DecodeArgs &a, int b, int h, in
   bulk_g2s(dst + I8_OFF_VMETA, static_cast<const uint8_t *>(a.L.ValueCache_metadata) + (pv * H + h) * META_HEAD, META_HEAD, bar);
 }
 
-__global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(DecodeArgs a, int n_items) {
+__global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(DecodeArgs a, int n_items, int n_edge) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
-  I8Smem &sm = *reinterpret_cast<I8Smem *>(smem_raw);
+  I8Smem &smem = *reinterpret_cast<I8Smem *>(smem_raw);
+  I8Main &sm = smem.u.m;
   const DecodePlan &P = a.P;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int gid = lane >> 2, tig = lane & 3;
@@ -155,8 +166,8 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
   const float kmagic = MAGIC_S + (hi_limb ? 128.0f : 0.0f);       // +128: rounds the low limb into the high one
 
   if (lane == 0) {
-    mbar_init(smem_u32(&ws.bar_k), 1);
-    mbar_init(smem_u32(&ws.bar_v), 1);
+    mbar_init(smem_u32(&smem.bar_k[warp]), 1);
+    mbar_init(smem_u32(&smem.bar_v[warp]), 1);
   }
   ws.inv[lane] = 0;
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -165,9 +176,20 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
   uint32_t seq = 0;          // page pairs consumed by this warp so far (mbarrier parity)
   bool dead = false;         // a bounded wait ran out: stop consuming, keep the block barriers uniform
   uint32_t inflight = 0;     // bit 0: a key-part copy is in flight, bit 1: a value-part copy (warp-uniform)
-  const uint32_t bar_k = smem_u32(&ws.bar_k), bar_v = smem_u32(&ws.bar_v), stage_u32 = smem_u32(&ws.stage[0]);
+  const uint32_t bar_k = smem_u32(&smem.bar_k[warp]), bar_v = smem_u32(&smem.bar_v[warp]), stage_u32 = smem_u32(&ws.stage[0]);
 
-  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+  // Page-pair items first (round-robin over the blocks), then the edge items: the blocks that run out of
+  // page pairs in the last round pick up edges first.
+  for (int item = blockIdx.x; item < n_items + n_edge; item += gridDim.x) {
+    if (item >= n_items) {
+      // ---- edge item: sink + tail of one (batch, kv-head), by the whole block ---- //
+      const int ebh = item - n_items;
+      __syncthreads();   // the previous item's merge buffer and query are no longer read
+      edge_item<4, I8_WARPS>(a, smem.u.e, ebh / H, ebh % H);
+      __syncthreads();
+      ws.inv[lane] = 0;  // the slot table was overwritten: keep its entries valid positions
+      continue;
+    }
     const int c = item % P.nchunk;
     const int bh = item / P.nchunk;
     const int h = bh % H, b = bh / H;
@@ -482,7 +504,7 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
   }
 }
 
-int launch_decode_paged_i8(const DecodeArgs &a, int n_items, int grid, cudaStream_t s) {
+int launch_decode_paged_i8(const DecodeArgs &a, int n_items, int n_edge, int grid, cudaStream_t s) {
   static int configured = -1;     // per-process opt-in to > 48 KB dynamic shared memory, done once per device
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return KITTY_E_CUDA;
@@ -492,7 +514,7 @@ int launch_decode_paged_i8(const DecodeArgs &a, int n_items, int grid, cudaStrea
       return KITTY_E_CUDA;
     configured = dev;
   }
-  decode_paged_i8_kernel<<<grid, I8_WARPS * 32, sizeof(I8Smem), s>>>(a, n_items);
+  decode_paged_i8_kernel<<<grid, I8_WARPS * 32, sizeof(I8Smem), s>>>(a, n_items, n_edge);
   return cudaGetLastError() == cudaSuccess ? KITTY_OK : KITTY_E_CUDA;
 }
 
