@@ -128,7 +128,9 @@ int kitty_flush(const kitty_layer *layer, const kitty_counts *counts, int32_t B,
 /* Bytes of scratch kitty_decode_attn needs for this problem size (negative
  * kitty_status on bad arguments).  The workspace is caller-owned device memory,
  * 256-byte aligned, ZERO-FILLED ONCE before its first use: its first word is a
- * sticky status that a kernel sets when a bounded wait runs out.  Calls that
+ * sticky status that a kernel sets when a bounded wait runs out, its second word
+ * the counter the streaming kernel hands work items out with (left at zero by
+ * every completed call).  Calls that
  * share a workspace must not overlap on the device.  The reference allocates its
  * scratch (the logits tensor) inside the call (kernels/kitty_attention.py:426-430). */
 int64_t kitty_decode_workspace_bytes(int32_t B, int32_t h_kv, int32_t h_q, int32_t max_pages);

@@ -40,7 +40,7 @@ struct DecodeArgs {
   int32_t q_dtype;
   float scale_log2;      // scaling * log2(e): logits live in the base-2 domain
   float *partials;       // [B*H, n_slots, G, PART]
-  int32_t *status;       // device word, set non-zero when a bounded wait ran out
+  int32_t *status;       // workspace header: [0] set non-zero when a bounded wait ran out, [1] item hand-out counter
 };
 
 // Merge n partials per row.  Row r's partial s lives at
@@ -52,6 +52,7 @@ struct MergeArgs {
   void *out;          // [rows, 128] of out_dtype, or null
   int32_t out_dtype;
   float *partial_out; // [rows, PART] or null: merged but un-normalised
+  int32_t *work_counter;  // or null: word the streaming kernel used to hand out items; reset to 0 here
 };
 
 int launch_decode_plain(const DecodeArgs &a, int items_per_bh, cudaStream_t s);

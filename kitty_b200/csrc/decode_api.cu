@@ -7,7 +7,7 @@
 
 namespace kitty {
 
-constexpr int64_t WS_HEADER = 256;   // bytes at the start of the workspace: sticky status word
+constexpr int64_t WS_HEADER = 256;   // bytes at the start of the workspace: sticky status word, item hand-out counter
 constexpr int PG_WARPS_HOST = 4;     // warps per block of the streaming kernel (pages per chunk come in multiples)
 
 static int sm_count() {
@@ -28,7 +28,7 @@ static int chunk_cap(int64_t bh_gt, int grid_max) {
 }
 
 // Pick pages-per-chunk so that the items fill `grid_max` resident blocks in whole waves.
-static void plan_chunks(int n_pages, int64_t bh_gt, int grid_max, int *ch_out, int *nchunk_out) {
+static void plan_chunks(int n_pages, int64_t bh_gt, int grid_max, bool dynamic, int *ch_out, int *nchunk_out) {
   if (n_pages <= 0) {
     *ch_out = PG_WARPS_HOST;
     *nchunk_out = 0;
@@ -43,7 +43,10 @@ static void plan_chunks(int n_pages, int64_t bh_gt, int grid_max, int *ch_out, i
     const int n = (n_pages + ch - 1) / ch;
     const int64_t items = bh_gt * n;
     const int64_t waves = (items + grid_max - 1) / grid_max;
-    const double cost = static_cast<double>(waves) * (ch / PG_WARPS_HOST + 1.5);   // +1.5: per-item prologue/merge
+    const double item_cost = ch / PG_WARPS_HOST + 1.5;                              // +1.5: per-item prologue/merge
+    // static round-robin: whole waves; dynamic hand-out: average load plus one item of tail
+    const double cost = dynamic ? (static_cast<double>(items) * item_cost / grid_max + item_cost)
+                                : static_cast<double>(waves) * item_cost;
     if (cost < best - 1e-9) {
       best = cost;
       best_ch = ch;
@@ -111,7 +114,7 @@ extern "C" int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *c
   const bool use_i8 = (impl == 0 && G <= 4);       // integer tensor-core kernel: 4 heads x (high, low) limb columns
   const int n_gt = use_i8 ? 1 : (G + 7) / 8;
   const int grid_max = (use_i8 ? 4 : 2) * sm_count();        // resident blocks per SM of the streaming kernel
-  plan_chunks(P.pe - P.pb, static_cast<int64_t>(B) * H * n_gt, grid_max, &P.ch, &P.nchunk);
+  plan_chunks(P.pe - P.pb, static_cast<int64_t>(B) * H * n_gt, grid_max, use_i8, &P.ch, &P.nchunk);
   P.fast_chunks = (impl != 1) ? 1 : 0;
   const int has_edge = (P.has_sink || P.has_tail) ? 1 : 0;
   if (P.fast_chunks) {            // slots: [edge?][chunks]
@@ -166,6 +169,7 @@ extern "C" int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *c
   m.out = out;
   m.out_dtype = out_dtype;
   m.partial_out = partial_out;
+  m.work_counter = a.status + 1;
   return launch_merge(m, s);
 }
 
@@ -183,6 +187,7 @@ extern "C" int kitty_lse_merge(const float *partials, int32_t n_parts, int64_t r
   m.out = out;
   m.out_dtype = out_dtype;
   m.partial_out = nullptr;
+  m.work_counter = nullptr;
   return launch_merge(m, static_cast<cudaStream_t>(stream));
 }
 

@@ -10,7 +10,7 @@
 //      reads 64 contiguous bytes of a row), packed key pages through the same
 //      code path as the streaming kernel;
 //   2. softmax statistics over the (small) edge, probabilities in place;
-//   3. P.V on the CUDA cores: a warp walks tokens (eight rows in flight), each lane
+//   3. P.V on the CUDA cores: a warp walks tokens (sixteen rows in flight), each lane
 //      owns 4 channels (one 8-byte load per row), then a fixed-order cross-warp reduction;
 //   4. one partial (acc, max, sum) per query head into the workspace slot.
 #pragma once
@@ -162,7 +162,7 @@ __device__ __forceinline__ void edge_item(const DecodeArgs &a, EdgeSmem<NW> &sm,
     if (r < C.Q_Buffer_Count_V) return qbufv + r * HD;
     return ringv + ((r - C.Q_Buffer_Count_V + C.Write_Offset_Local_V) & (PAGE - 1)) * HD;
   };
-  constexpr int UNR = 8;
+  constexpr int UNR = 16;
   for (int e0 = warp; e0 < ne; e0 += UNR * EDGE_WARPS) {
     uint2 raw[UNR];
 #pragma unroll

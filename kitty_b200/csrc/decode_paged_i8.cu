@@ -76,6 +76,7 @@ struct I8Smem {
     EdgeSmem<I8_WARPS> e;
   } u;
   __align__(8) unsigned long long bar_k[I8_WARPS], bar_v[I8_WARPS];
+  int next_item;
 };
 static_assert(I8_WARPS * 4 * PART * 4 <= I8_STAGE_BYTES, "merge buffer overlays warp 0's stage");
 static_assert(sizeof(I8Smem) <= 56 * 1024, "four blocks per SM");
@@ -178,13 +179,23 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
   uint32_t inflight = 0;     // bit 0: a key-part copy is in flight, bit 1: a value-part copy (warp-uniform)
   const uint32_t bar_k = smem_u32(&smem.bar_k[warp]), bar_v = smem_u32(&smem.bar_v[warp]), stage_u32 = smem_u32(&ws.stage[0]);
 
-  // Page-pair items first (round-robin over the blocks), then the edge items: the blocks that run out of
-  // page pairs in the last round pick up edges first.
-  for (int item = blockIdx.x; item < n_items + n_edge; item += gridDim.x) {
-    if (item >= n_items) {
+  // Items are handed out dynamically (a work counter in the workspace header, zero on entry and reset by
+  // the merge kernel that always follows), so blocks stay busy until the list is empty.  Edge items are
+  // spread evenly through the sequence (position i holds an edge item when floor((i+1)*n_edge/total) >
+  // floor(i*n_edge/total)): at any time most blocks stream pages while a few reduce a latency-bound edge.
+  const long long total = static_cast<long long>(n_items) + n_edge;
+  for (;;) {
+    __syncthreads();     // the previous item's merge buffer, query and work index are no longer read
+    if (tid == 0) smem.next_item = atomicAdd(a.status + 1, 1);
+    __syncthreads();
+    const int it = smem.next_item;
+    if (it >= total) break;
+    const int e_before = static_cast<int>(static_cast<long long>(it) * n_edge / total);
+    const int e_after = static_cast<int>((static_cast<long long>(it) + 1) * n_edge / total);
+    const int item = it - e_before;        // index among the page-pair items
+    if (e_after > e_before) {
       // ---- edge item: sink + tail of one (batch, kv-head), by the whole block ---- //
-      const int ebh = item - n_items;
-      __syncthreads();   // the previous item's merge buffer and query are no longer read
+      const int ebh = e_before;
       edge_item<4, I8_WARPS>(a, smem.u.e, ebh / H, ebh % H);
       __syncthreads();
       ws.inv[lane] = 0;  // the slot table was overwritten: keep its entries valid positions
@@ -196,7 +207,6 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
     const int p0 = P.pb + c * P.ch;
     const int p1 = min(P.pe, p0 + P.ch);
 
-    __syncthreads();   // previous item's merge buffer (overlaying warp 0's stage) and query are no longer read
     // ---- query of head `warp`: maximum, then q / qmax in arranged order ---- //
     {
       float qv[4], mx = 0.f;

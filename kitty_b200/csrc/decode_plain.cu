@@ -228,6 +228,7 @@ __global__ void __launch_bounds__(128) merge_kernel(MergeArgs a) {
     }
     for (; s < nn; ++s) A = fmaf(p[s * a.stride_part], w_s[s], A);
   }
+  if (a.work_counter != nullptr && r == 0 && c == 0) *a.work_counter = 0;   // ready for the next call's item hand-out
   if (a.partial_out) {
     float *o = a.partial_out + r * PART;
     o[c] = A;
