@@ -50,6 +50,8 @@ def parse():
                     help="decode (the headline metric), quantize (bulk prefill quantize/pack throughput) or e2e "
                          "(Llama-3-8B-shaped random-init decoder: batch 16, 4096-token prompts, 256 greedy steps)")
     ap.add_argument("--layers", type=int, default=32, help="decoder layers of the e2e workload")
+    ap.add_argument("--graph", action="store_true", help="e2e workload: replay the decode step from a CUDA graph")
+    ap.add_argument("--e2e-batch", type=int, default=16, help="batch of the e2e workload")
     return ap.parse_args()
 
 
@@ -269,11 +271,11 @@ def e2e_workload(args):
     from transformers import LlamaConfig, LlamaForCausalLM
 
     import kitty_b200 as kb
-    from kitty_b200.hf_adapter import greedy_decode, patch_model
+    from kitty_b200.hf_adapter import GraphedDecoder, patch_model
 
     device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(device)
-    B, L, steps = 16, 4096, 256
+    B, L, steps = args.e2e_batch, 4096, 256
     cfg = LlamaConfig(hidden_size=4096, intermediate_size=14336, num_hidden_layers=args.layers, num_attention_heads=32,
                       num_key_value_heads=8, head_dim=128, vocab_size=128256, max_position_embeddings=8192,
                       rope_theta=500000.0, tie_word_embeddings=False)
@@ -297,14 +299,30 @@ def e2e_workload(args):
             tok = model.lm_head(hs[:, -1:, :]).argmax(-1)
             torch.cuda.synchronize()
             t1 = time.perf_counter()
-            for s_ in range(1, steps):
-                p = torch.full((1, 1), L + s_ - 1, device=device, dtype=torch.long)
-                hs = model.model(input_ids=tok, position_ids=p, past_key_values=cache, use_cache=True).last_hidden_state
-                tok = model.lm_head(hs).argmax(-1)
+            if args.graph:
+                dec = GraphedDecoder(model, cache, B)
+                dec.tok.copy_(tok)
+                dec.pos.fill_(L)
+                for s_ in range(1, steps):
+                    if s_ == steps // 2:
+                        torch.cuda.synchronize()
+                        th = time.perf_counter()
+                    dec.step()
+            else:
+                for s_ in range(1, steps):
+                    if s_ == steps // 2:
+                        torch.cuda.synchronize()
+                        th = time.perf_counter()
+                    p = torch.full((1, 1), L + s_ - 1, device=device, dtype=torch.long)
+                    hs = model.model(input_ids=tok, position_ids=p, past_key_values=cache, use_cache=True).last_hidden_state
+                    tok = model.lm_head(hs).argmax(-1)
             torch.cuda.synchronize()
         t2 = time.perf_counter()
         del cache
+        steady.append((t2 - th) / (steps - steps // 2) * 1e3)
         return t1 - t0, t2 - t1
+
+    steady = []
 
     run()                                   # warm-up generate (fresh cache per run, as the reference benchmark does)
     pre, dec = zip(*[run() for _ in range(max(1, min(args.steps, 3)))])
@@ -312,8 +330,9 @@ def e2e_workload(args):
     print(json.dumps({"metric": "e2e_decode_tokens_per_s", "value": B * (steps - 1) / dec_s, "unit": "tokens/s",
                       "n_gpus": 1, "steps": steps, "ms_per_step": dec_s / (steps - 1) * 1e3, "higher_is_better": True,
                       "dtype": "bf16", "data": "synthetic",
-                      "config": {"workload": f"random-init Llama-3-8B shape, {args.layers} layers, batch 16, prompt 4096, "
-                                             "256 greedy steps, KittyCache", "prefill_s": pre_s, "decode_s": dec_s,
+                      "config": {"workload": f"random-init Llama-3-8B shape, {args.layers} layers, batch {B}, prompt 4096, "
+                                             "256 greedy steps, KittyCache" + (", decode steps replayed from one CUDA graph (capture included)"
+                                                                              if args.graph else ""), "prefill_s": pre_s, "decode_s": dec_s, "steady_ms_per_step": min(steady[1:]),
                                  "generate_s": pre_s + dec_s}}))
 
 

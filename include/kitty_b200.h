@@ -160,6 +160,45 @@ int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *counts, cons
                       int64_t workspace_bytes, int32_t page_begin, int32_t page_end, int32_t flags,
                       float *partial_out, int impl, void *stream);
 
+/* ---- Decode step with device-resident state (CUDA-graph friendly) ------------------------
+ * The reference passes its counters to every kernel as Python ints
+ * (kernels/kitty_attention.py:458-460, 510-514), which bakes them into a captured graph.  Here the
+ * per-step state lives in a small device block that every kernel of the step reads; a captured
+ * graph stays valid for the life of the cache because no launch argument or launch dimension
+ * depends on the step.  All layers of a cache share the block (their counters are identical).
+ *
+ *   host, once per token:   kitty_plan_step(...) fills a kitty_step_state on the host and
+ *                           writes it to the device block (one small launch on the stream: the
+ *                           160 bytes travel as a kernel argument, so no host buffer has to
+ *                           stay untouched until the copy runs).
+ *   per layer (capturable): kitty_decode_step(...) = append + attention + merge + flush-if-due.
+ *   host, after the token:  advance the counters as kvcache/kitty.py:102-123, 201-234 does
+ *                           (kitty_plan_step returns the new counters in state->next).
+ * Limits: groups of up to 4 query heads per KV head (the int8 streaming kernel), whole sequence
+ * on one GPU, in-kernel channel selection. */
+typedef struct {
+  kitty_counts before;   /* state before this step's append                                        */
+  kitty_counts after;    /* after the append: what the attention kernels see                       */
+  kitty_counts next;     /* after the step's flushes: `before` of the next step (host use)         */
+  int32_t pb, pe, ch, nchunk, has_sink, has_tail, n_slots, n_tiles, chunk_slot0, edge_slot;
+  int32_t n_items, n_edge, flush_k, flush_v;
+  int32_t reserved[2];
+} kitty_step_state;      /* 160 bytes */
+
+/* Fills *state (host memory) for one decode step of a cache whose counters are *before and, when
+ * device_state is not null, stores the same 160 bytes there in stream order. */
+int kitty_plan_step(const kitty_layer *layer, const kitty_counts *before, int32_t B, int32_t h_q,
+                    kitty_step_state *state, kitty_step_state *device_state, void *stream);
+
+/* One layer's decode step from the device-resident state: kitty_append, kitty_decode_attn
+ * (impl 0, whole sequence) and kitty_flush in four launches whose arguments do not depend on the
+ * step.  key/value: [B, H, 1, 128] (element strides as for kitty_append); query [B, h_q, 1, 128]
+ * contiguous; out [B, 1, h_q, 128] contiguous; workspace as for kitty_decode_attn. */
+int kitty_decode_step(const kitty_layer *layer, const kitty_step_state *device_state, const void *key,
+                      const void *value, int kv_dtype, int64_t k_stride_b, int64_t k_stride_h, int64_t v_stride_b,
+                      int64_t v_stride_h, const void *query, int q_dtype, int32_t B, int32_t h_q, float scaling,
+                      void *out, int out_dtype, void *workspace, int64_t workspace_bytes, int div_mode, void *stream);
+
 /* Size in bytes of the scratch array built into the library for kitty_decode_attn_static. */
 #define KITTY_STATIC_SCRATCH_BYTES (8u << 20)
 

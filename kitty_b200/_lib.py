@@ -21,7 +21,7 @@ DIV_IEEE, DIV_FULL = 0, 1
 EXPORTS = [
     "kitty_version", "kitty_strerror", "kitty_quant_pack_k", "kitty_quant_pack_v", "kitty_prefill_tails",
     "kitty_append", "kitty_flush", "kitty_decode_workspace_bytes", "kitty_workspace_status", "kitty_decode_attn",
-    "kitty_lse_merge", "kitty_decode_attn_static",
+    "kitty_lse_merge", "kitty_decode_attn_static", "kitty_plan_step", "kitty_decode_step",
 ]
 
 
@@ -39,6 +39,14 @@ class KittyCounts(C.Structure):
     _fields_ = [(n, C.c_int32) for n in
                 ("PageCount_K", "PageCount_V", "Sink_Count", "Q_Buffer_Count_K", "Q_Buffer_Count_V", "Local_Count_V",
                  "Write_Offset_Local_V", "reserved")]
+
+
+class KittyStepState(C.Structure):
+    """struct kitty_step_state"""
+    _fields_ = [("before", KittyCounts), ("after", KittyCounts), ("next", KittyCounts)] + \
+               [(n, C.c_int32) for n in ("pb", "pe", "ch", "nchunk", "has_sink", "has_tail", "n_slots", "n_tiles",
+                                         "chunk_slot0", "edge_slot", "n_items", "n_edge", "flush_k", "flush_v",
+                                         "reserved0", "reserved1")]
 
 
 class KittyError(RuntimeError):
@@ -89,6 +97,12 @@ def lib() -> C.CDLL:
     L.kitty_decode_attn_static.restype = C.c_int
     L.kitty_decode_attn_static.argtypes = [C.POINTER(KittyLayer), C.POINTER(KittyCounts), vp, C.c_int, i32, i32,
                                            C.c_float, vp, C.c_int, i32, i32, i32, vp, C.c_int, vp, vp]
+    L.kitty_plan_step.restype = C.c_int
+    L.kitty_plan_step.argtypes = [C.POINTER(KittyLayer), C.POINTER(KittyCounts), i32, i32, C.POINTER(KittyStepState),
+                                  vp, vp]
+    L.kitty_decode_step.restype = C.c_int
+    L.kitty_decode_step.argtypes = [C.POINTER(KittyLayer), vp, vp, vp, C.c_int, i64, i64, i64, i64, vp, C.c_int, i32,
+                                    i32, C.c_float, vp, C.c_int, vp, i64, C.c_int, vp]
     L.kitty_lse_merge.restype = C.c_int
     L.kitty_lse_merge.argtypes = [vp, i32, i64, vp, C.c_int, vp]
     _lib = L

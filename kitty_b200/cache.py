@@ -42,6 +42,8 @@ class KittyCache(Cache):
         self.selection = selection
         self.div_mode = div_mode
         self._kitty_max_batch, self._kitty_max_length = max_batch_size, max_length
+        self._step_dev: Optional[torch.Tensor] = None       # device block of the device-resident decode step
+        self._step_host = None
         self.kv_cache: list[KVCache_Layer] = [
             KVCache_Layer(MAX_BS=max_batch_size, MAX_LEN=max_length, H_KV=self.num_key_value_heads, D=self.head_dim,
                           D_BOOSTED=self.d_boosted, LOW_BIT=self.low_bit, HIGH_BIT=self.high_bit,
@@ -151,6 +153,73 @@ class KittyCache(Cache):
         if fv:
             lay.PageCount_V += 1
             lay.Q_Buffer_Count_V = 0
+
+    # -- decode step with device-resident state (for CUDA-graph capture) ----------------- #
+    # The three calls of a decode step (update, kitty_attention_forward, quantize_decode) pass the
+    # counters by value, so their launches differ from token to token.  In this mode the counters and
+    # the split-KV plan of the token live in one 160-byte device block that every kernel reads:
+    #     cache.plan_step(B, H_Q)            host, once per token (one tiny launch writes the block)
+    #     cache.step_layer(i, k, v, q, ...)  per layer; four launches with step-independent arguments
+    #     cache.finish_step()                host, once per token: counters := state after the flushes
+    # step_layer may be captured in a CUDA graph and replayed for every later token.
+    def plan_step(self, batch: int, h_q: int) -> "_lib.KittyStepState":
+        import ctypes
+
+        if self.selection != "fused":
+            raise ValueError("the device-resident decode step selects channels inside the flush kernel "
+                             "(selection='fused')")
+        lay0 = self.kv_cache[0]
+        ref = self._counter_tuple(lay0)
+        for lay in self.kv_cache[1:]:
+            if self._counter_tuple(lay) != ref:
+                raise ValueError("the layers of the cache are not at the same position")
+        if self._step_dev is None:
+            self._step_dev = torch.zeros(ctypes.sizeof(_lib.KittyStepState), dtype=torch.uint8, device=lay0.device)
+        st = _lib.KittyStepState()
+        rc = _lib.lib().kitty_plan_step(lay0.c_layer(), lay0.c_counts(), batch, h_q, ctypes.byref(st),
+                                        self._step_dev.data_ptr(), _lib.stream_ptr(lay0.device))
+        _lib.check(rc, "kitty_plan_step")
+        self._step_host = st
+        return st
+
+    def step_layer(self, layer_idx: int, key_states: torch.Tensor, value_states: torch.Tensor, query: torch.Tensor,
+                   scaling: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """append + attention + flush-if-due of one layer from the planned state.  key/value [B, H, 1, 128],
+        query [B, H_Q, 1, 128] contiguous.  Returns [B, 1, H_Q, 128] in the query's dtype."""
+        if self._step_dev is None:
+            raise RuntimeError("call plan_step() first")
+        lay = self.kv_cache[layer_idx]
+        B, H_Q, t_query, D = query.shape
+        assert t_query == 1 and query.is_contiguous()
+        assert key_states.shape[-2] == 1 and value_states.shape[-2] == 1
+        assert key_states.stride(-1) == 1 and value_states.stride(-1) == 1 and key_states.dtype == value_states.dtype
+        if out is None:
+            out = torch.empty((B, 1, H_Q, D), dtype=query.dtype, device=query.device)
+        ws = lay.workspace(lay.MAX_BS, H_Q)
+        rc = _lib.lib().kitty_decode_step(lay.c_layer(), self._step_dev.data_ptr(), key_states.data_ptr(),
+                                          value_states.data_ptr(), _lib.dtype_code(key_states.dtype),
+                                          key_states.stride(0), key_states.stride(1), value_states.stride(0),
+                                          value_states.stride(1), query.data_ptr(), _lib.dtype_code(query.dtype), B,
+                                          H_Q, float(scaling), out.data_ptr(), _lib.dtype_code(out.dtype),
+                                          ws.data_ptr(), ws.numel(), self.div_mode, _lib.stream_ptr(query.device))
+        _lib.check(rc, "kitty_decode_step")
+        return out
+
+    def finish_step(self) -> None:
+        st = self._step_host
+        if st is None:
+            raise RuntimeError("call plan_step() first")
+        n = st.next
+        for lay in self.kv_cache:
+            lay.PageCount_K, lay.PageCount_V, lay.Sink_Count = n.PageCount_K, n.PageCount_V, n.Sink_Count
+            lay.Q_Buffer_Count_K, lay.Q_Buffer_Count_V = n.Q_Buffer_Count_K, n.Q_Buffer_Count_V
+            lay.Local_Count_V, lay.Write_Offset_Local_V = n.Local_Count_V, n.Write_Offset_Local_V
+        self._step_host = None
+
+    @staticmethod
+    def _counter_tuple(lay) -> tuple:
+        return (lay.PageCount_K, lay.PageCount_V, lay.Sink_Count, lay.Q_Buffer_Count_K, lay.Q_Buffer_Count_V,
+                lay.Local_Count_V, lay.Write_Offset_Local_V)
 
     def get_seq_length(self, layer_idx: int = 0) -> int:
         return self.kv_cache[layer_idx].get_total_length()

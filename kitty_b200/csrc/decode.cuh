@@ -41,6 +41,7 @@ struct DecodeArgs {
   float scale_log2;      // scaling * log2(e): logits live in the base-2 domain
   float *partials;       // [B*H, n_slots, G, PART]
   int32_t *status;       // workspace header: [0] set non-zero when a bounded wait ran out, [1] item hand-out counter
+  const kitty_step_state *dyn;   // or null.  Non-null: plan, counters and item counts are read from it on the device
 };
 
 // Merge n partials per row.  Row r's partial s lives at
@@ -53,12 +54,16 @@ struct MergeArgs {
   int32_t out_dtype;
   float *partial_out; // [rows, PART] or null: merged but un-normalised
   int32_t *work_counter;  // or null: word the streaming kernel used to hand out items; reset to 0 here
+  const kitty_step_state *dyn;   // or null.  Non-null: the number of slots is read from it on the device
 };
 
 int launch_decode_plain(const DecodeArgs &a, int items_per_bh, cudaStream_t s);
 int launch_decode_paged(const DecodeArgs &a, int n_items, int n_gt, int grid, cudaStream_t s);
 int launch_decode_paged_i8(const DecodeArgs &a, int n_items, int n_edge, int grid, cudaStream_t s);
 int launch_decode_edge(const DecodeArgs &a, cudaStream_t s);
+int launch_append_dyn(const kitty_layer &L, const kitty_step_state *dyn, const void *key, const void *value, int dtype,
+                      int64_t ksb, int64_t ksh, int64_t vsb, int64_t vsh, int32_t B, cudaStream_t s);
+int launch_flush_dyn(const kitty_layer &L, const kitty_step_state *dyn, int32_t B, int div_mode, cudaStream_t s);
 int launch_merge(const MergeArgs &m, cudaStream_t s);
 
 __device__ __forceinline__ float load_q(const void *q, int dtype, int64_t i) {

@@ -134,6 +134,7 @@ extern "C" int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *c
   a.q_dtype = q_dtype;
   a.scale_log2 = scaling * 1.4426950408889634f;
   a.status = static_cast<int32_t *>(workspace);
+  a.dyn = nullptr;
   a.partials = reinterpret_cast<float *>(static_cast<uint8_t *>(workspace) + WS_HEADER);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
@@ -170,6 +171,7 @@ extern "C" int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *c
   m.out_dtype = out_dtype;
   m.partial_out = partial_out;
   m.work_counter = a.status + 1;
+  m.dyn = nullptr;
   return launch_merge(m, s);
 }
 
@@ -188,7 +190,147 @@ extern "C" int kitty_lse_merge(const float *partials, int32_t n_parts, int64_t r
   m.out_dtype = out_dtype;
   m.partial_out = nullptr;
   m.work_counter = nullptr;
+  m.dyn = nullptr;
   return launch_merge(m, static_cast<cudaStream_t>(stream));
+}
+
+// ------------------------------------------------------------------------- //
+// Decode step with device-resident state
+// ------------------------------------------------------------------------- //
+static bool counts_ok(const kitty_layer *layer, const kitty_counts &C) {
+  if (C.PageCount_K < 0 || C.PageCount_V < 0 || C.PageCount_K > layer->max_page || C.PageCount_V > layer->max_page ||
+      C.Sink_Count < 0 || C.Sink_Count > SINK || C.Q_Buffer_Count_K < 0 || C.Q_Buffer_Count_K > PAGE ||
+      C.Q_Buffer_Count_V < 0 || C.Q_Buffer_Count_V > PAGE || C.Local_Count_V < 0 || C.Local_Count_V > PAGE ||
+      C.Write_Offset_Local_V < 0 || C.Write_Offset_Local_V >= PAGE)
+    return false;
+  const int64_t tk = static_cast<int64_t>(C.PageCount_K) * PAGE + C.Q_Buffer_Count_K;
+  const int64_t tv = static_cast<int64_t>(C.PageCount_V) * PAGE + C.Q_Buffer_Count_V + C.Local_Count_V;
+  return tk == tv && C.PageCount_V <= C.PageCount_K && !(C.Sink_Count < SINK && tk != 0);
+}
+
+__global__ void store_step_state_kernel(kitty_step_state st, kitty_step_state *dst) {
+  const int32_t *src = reinterpret_cast<const int32_t *>(&st);
+  const int n = static_cast<int>(sizeof(kitty_step_state) / sizeof(int32_t));
+  if (threadIdx.x < n) reinterpret_cast<int32_t *>(dst)[threadIdx.x] = src[threadIdx.x];
+}
+
+extern "C" int kitty_plan_step(const kitty_layer *layer, const kitty_counts *before, int32_t B, int32_t h_q,
+                               kitty_step_state *state, kitty_step_state *device_state, void *stream) {
+  if (!layer || !before || !state) return KITTY_E_BADARG;
+  if (layer->head_dim != HD || layer->page_size != PAGE || layer->d_boost != DB || layer->sink_size != SINK)
+    return KITTY_E_BADSHAPE;
+  const int H = layer->h_kv;
+  if (B <= 0 || B > layer->max_bs || H <= 0 || h_q <= 0 || h_q % H != 0) return KITTY_E_BADARG;
+  const int G = h_q / H;
+  if (G > 4) return KITTY_E_BADSHAPE;
+  if (!counts_ok(layer, *before)) return KITTY_E_BADARG;
+  kitty_step_state &st = *state;
+  st = kitty_step_state{};
+  st.before = *before;
+  // append (kvcache/kitty.py:102-123)
+  kitty_counts c = *before;
+  if (c.Sink_Count < SINK) {
+    c.Sink_Count += 1;
+  } else {
+    if (c.Q_Buffer_Count_K >= PAGE) return KITTY_E_BADARG;
+    c.Q_Buffer_Count_K += 1;
+    if (c.Local_Count_V < PAGE) {
+      c.Local_Count_V += 1;
+    } else {
+      if (c.Q_Buffer_Count_V >= PAGE) return KITTY_E_BADARG;
+      c.Q_Buffer_Count_V += 1;
+      c.Write_Offset_Local_V = (c.Write_Offset_Local_V + 1) % PAGE;
+    }
+  }
+  st.after = c;
+  // flush (kvcache/kitty.py:201-234)
+  st.flush_k = (c.Q_Buffer_Count_K == PAGE) ? 1 : 0;
+  st.flush_v = (c.Q_Buffer_Count_V == PAGE) ? 1 : 0;
+  if ((st.flush_k && c.PageCount_K >= layer->max_page) || (st.flush_v && c.PageCount_V >= layer->max_page))
+    return KITTY_E_BADARG;
+  kitty_counts n = c;
+  if (st.flush_k) { n.PageCount_K += 1; n.Q_Buffer_Count_K = 0; }
+  if (st.flush_v) { n.PageCount_V += 1; n.Q_Buffer_Count_V = 0; }
+  st.next = n;
+  // plan of the attention call (whole sequence, int8 streaming kernel)
+  const int pv = c.PageCount_V;
+  const int64_t tk = static_cast<int64_t>(c.PageCount_K) * PAGE + c.Q_Buffer_Count_K;
+  st.pb = 0;
+  st.pe = pv;
+  st.n_tiles = 1 + static_cast<int>((tk + PAGE - 1) / PAGE);
+  st.has_sink = c.Sink_Count > 0 ? 1 : 0;
+  st.has_tail = (st.n_tiles - 1 - pv) > 0 ? 1 : 0;
+  const int grid_max = 4 * sm_count();
+  plan_chunks(pv, static_cast<int64_t>(B) * H, grid_max, true, &st.ch, &st.nchunk);
+  const int has_edge = (st.has_sink || st.has_tail) ? 1 : 0;
+  st.n_slots = has_edge + st.nchunk;
+  st.chunk_slot0 = has_edge;
+  st.edge_slot = 0;
+  st.n_items = B * H * st.nchunk;
+  st.n_edge = has_edge ? B * H : 0;
+  if (device_state != nullptr) {
+    if ((reinterpret_cast<uintptr_t>(device_state) & 15u) != 0) return KITTY_E_BADARG;
+    store_step_state_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(st, device_state);
+    if (cudaGetLastError() != cudaSuccess) return KITTY_E_CUDA;
+  }
+  return KITTY_OK;
+}
+
+extern "C" int kitty_decode_step(const kitty_layer *layer, const kitty_step_state *device_state, const void *key,
+                                 const void *value, int kv_dtype, int64_t k_stride_b, int64_t k_stride_h,
+                                 int64_t v_stride_b, int64_t v_stride_h, const void *query, int q_dtype, int32_t B,
+                                 int32_t h_q, float scaling, void *out, int out_dtype, void *workspace,
+                                 int64_t workspace_bytes, int div_mode, void *stream) {
+  if (!layer || !device_state || !key || !value || !query || !out || !workspace) return KITTY_E_BADARG;
+  if (layer->head_dim != HD || layer->page_size != PAGE || layer->d_boost != DB || layer->sink_size != SINK)
+    return KITTY_E_BADSHAPE;
+  const int H = layer->h_kv;
+  if (B <= 0 || B > layer->max_bs || B > 65535 || H <= 0 || H > 65535 || h_q <= 0 || h_q % H != 0) return KITTY_E_BADARG;
+  const int G = h_q / H;
+  if (G > 4) return KITTY_E_BADSHAPE;
+  if (kv_dtype < KITTY_F16 || kv_dtype > KITTY_F32 || q_dtype < KITTY_F16 || q_dtype > KITTY_F32 ||
+      out_dtype < KITTY_F16 || out_dtype > KITTY_F32)
+    return KITTY_E_BADARG;
+  if (div_mode != KITTY_DIV_IEEE && div_mode != KITTY_DIV_FULL) return KITTY_E_BADARG;
+  const int64_t q16 = 16 / (kv_dtype == KITTY_F32 ? 4 : 2);
+  if ((reinterpret_cast<uintptr_t>(key) & 15u) || (reinterpret_cast<uintptr_t>(value) & 15u) || k_stride_b % q16 ||
+      k_stride_h % q16 || v_stride_b % q16 || v_stride_h % q16)
+    return KITTY_E_BADARG;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return KITTY_E_BADARG;
+  if (workspace_bytes < kitty_decode_workspace_bytes(B, H, h_q, layer->max_page)) return KITTY_E_WORKSPACE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  if (int rc = launch_append_dyn(*layer, device_state, key, value, kv_dtype, k_stride_b, k_stride_h, v_stride_b,
+                                 v_stride_h, B, s))
+    return rc;
+  DecodeArgs a;
+  a.L = *layer;
+  a.C = kitty_counts{};
+  a.P = DecodePlan{};
+  a.P.B = B; a.P.H = H; a.P.G = G; a.P.h_q = h_q;
+  a.P.fast_chunks = 1;
+  a.q = query;
+  a.q_dtype = q_dtype;
+  a.scale_log2 = scaling * 1.4426950408889634f;
+  a.status = static_cast<int32_t *>(workspace);
+  a.partials = reinterpret_cast<float *>(static_cast<uint8_t *>(workspace) + WS_HEADER);
+  a.dyn = device_state;
+  const int grid = 4 * sm_count();                      // fixed: the items are handed out on the device
+  if (int rc = launch_decode_paged_i8(a, 0, 0, grid, s)) return rc;
+  MergeArgs m;
+  m.partials = a.partials;
+  m.rows = static_cast<int64_t>(B) * h_q;
+  m.stride_part = static_cast<int64_t>(G) * PART;
+  m.n = 0;
+  m.gm = G;
+  m.ns = 0;
+  m.out = out;
+  m.out_dtype = out_dtype;
+  m.partial_out = nullptr;
+  m.work_counter = a.status + 1;
+  m.dyn = device_state;
+  if (int rc = launch_merge(m, s)) return rc;
+  return launch_flush_dyn(*layer, device_state, B, div_mode, s);
 }
 
 extern "C" int kitty_workspace_status(const void *workspace, int32_t *host_status, void *stream) {

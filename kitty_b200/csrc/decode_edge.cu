@@ -10,7 +10,7 @@ template <int NG>
 __global__ void __launch_bounds__(EDGE_KERNEL_WARPS * 32) decode_edge_kernel(DecodeArgs a) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   EdgeSmem<EDGE_KERNEL_WARPS> &sm = *reinterpret_cast<EdgeSmem<EDGE_KERNEL_WARPS> *>(smem_raw);
-  edge_item<NG, EDGE_KERNEL_WARPS>(a, sm, blockIdx.y, blockIdx.x);
+  edge_item<NG, EDGE_KERNEL_WARPS>(a, a.P, a.C, sm, blockIdx.y, blockIdx.x);
 }
 
 int launch_decode_edge(const DecodeArgs &a, cudaStream_t s) {

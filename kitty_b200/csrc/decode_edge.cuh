@@ -36,10 +36,9 @@ struct EdgeSmem {
 // Reduces the edge of one (batch b, kv-head h) with the NW warps of the calling block and writes the
 // partial into the workspace slot P.edge_slot.  Every thread of the block must call it.
 template <int NG, int NW>
-__device__ __forceinline__ void edge_item(const DecodeArgs &a, EdgeSmem<NW> &sm, int b, int h) {
+__device__ __forceinline__ void edge_item(const DecodeArgs &a, const DecodePlan &P, const kitty_counts &C,
+                                          EdgeSmem<NW> &sm, int b, int h) {
   constexpr int EDGE_WARPS = NW;
-  const DecodePlan &P = a.P;
-  const kitty_counts &C = a.C;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
   const int H = P.H, G = P.G;
   const int64_t bh = static_cast<int64_t>(b) * H + h;

@@ -77,6 +77,10 @@ struct I8Smem {
   } u;
   __align__(8) unsigned long long bar_k[I8_WARPS], bar_v[I8_WARPS];
   int next_item;
+  // copy of the device-resident step state (plan, counters, item counts) when the launch carries one
+  DecodePlan dyn_plan;
+  kitty_counts dyn_counts;
+  int dyn_items, dyn_edge;
 };
 static_assert(I8_WARPS * 4 * PART * 4 <= I8_STAGE_BYTES, "merge buffer overlays warp 0's stage");
 static_assert(sizeof(I8Smem) <= 56 * 1024, "four blocks per SM");
@@ -152,11 +156,28 @@ __device__ __forceinline__ void i8_issue_v(const DecodeArgs &a, int b, int h, in
   bulk_g2s(dst + I8_OFF_VMETA, static_cast<const uint8_t *>(a.L.ValueCache_metadata) + (pv * H + h) * META_HEAD, META_HEAD, bar);
 }
 
-__global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(DecodeArgs a, int n_items, int n_edge) {
+// kDyn: the plan, the counters and the item counts come from the device block a.dyn (copied to shared
+// memory once per block) instead of the launch arguments.
+template <bool kDyn>
+__global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(DecodeArgs a, int n_items_arg, int n_edge_arg) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   I8Smem &smem = *reinterpret_cast<I8Smem *>(smem_raw);
   I8Main &sm = smem.u.m;
-  const DecodePlan &P = a.P;
+  if (kDyn && threadIdx.x == 0) {
+    const kitty_step_state &d = *a.dyn;
+    DecodePlan p = a.P;
+    p.pb = d.pb; p.pe = d.pe; p.ch = d.ch; p.nchunk = d.nchunk; p.has_sink = d.has_sink; p.has_tail = d.has_tail;
+    p.n_slots = d.n_slots; p.n_tiles = d.n_tiles; p.chunk_slot0 = d.chunk_slot0; p.edge_slot = d.edge_slot;
+    smem.dyn_plan = p;
+    smem.dyn_counts = d.after;
+    smem.dyn_items = d.n_items;
+    smem.dyn_edge = d.n_edge;
+  }
+  if (kDyn) __syncthreads();
+  const DecodePlan &P = kDyn ? smem.dyn_plan : a.P;
+  const kitty_counts &C = kDyn ? smem.dyn_counts : a.C;
+  const int n_items = kDyn ? smem.dyn_items : n_items_arg;
+  const int n_edge = kDyn ? smem.dyn_edge : n_edge_arg;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int gid = lane >> 2, tig = lane & 3;
   const int H = P.H, G = P.G;
@@ -196,7 +217,7 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
     if (e_after > e_before) {
       // ---- edge item: sink + tail of one (batch, kv-head), by the whole block ---- //
       const int ebh = e_before;
-      edge_item<4, I8_WARPS>(a, smem.u.e, ebh / H, ebh % H);
+      edge_item<4, I8_WARPS>(a, P, C, smem.u.e, ebh / H, ebh % H);
       __syncthreads();
       ws.inv[lane] = 0;  // the slot table was overwritten: keep its entries valid positions
       continue;
@@ -519,12 +540,17 @@ int launch_decode_paged_i8(const DecodeArgs &a, int n_items, int n_edge, int gri
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return KITTY_E_CUDA;
   if (configured != dev) {
-    if (cudaFuncSetAttribute(decode_paged_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(decode_paged_i8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(sizeof(I8Smem))) != cudaSuccess ||
+        cudaFuncSetAttribute(decode_paged_i8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(sizeof(I8Smem))) != cudaSuccess)
       return KITTY_E_CUDA;
     configured = dev;
   }
-  decode_paged_i8_kernel<<<grid, I8_WARPS * 32, sizeof(I8Smem), s>>>(a, n_items, n_edge);
+  if (a.dyn != nullptr)
+    decode_paged_i8_kernel<true><<<grid, I8_WARPS * 32, sizeof(I8Smem), s>>>(a, n_items, n_edge);
+  else
+    decode_paged_i8_kernel<false><<<grid, I8_WARPS * 32, sizeof(I8Smem), s>>>(a, n_items, n_edge);
   return cudaGetLastError() == cudaSuccess ? KITTY_OK : KITTY_E_CUDA;
 }
 

@@ -192,6 +192,7 @@ __global__ void __launch_bounds__(128) merge_kernel(MergeArgs a) {
   __shared__ float red[4];
   const int64_t r = blockIdx.x;
   const int c = threadIdx.x, lane = c & 31, warp = c >> 5;
+  if (a.dyn != nullptr) a.n = a.ns = a.dyn->n_slots;
   const float *base = a.partials + ((r / a.gm) * a.ns * a.gm + r % a.gm) * PART;
   float M = -INFINITY, A = 0.f, Lsum = 0.f;
   for (int s0 = 0; s0 < a.n; s0 += 128) {           // chunks of 128 slots (one chunk in practice)

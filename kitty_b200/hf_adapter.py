@@ -84,3 +84,83 @@ def greedy_decode(model, input_ids: torch.Tensor, steps: int, cache):
         tok = model.lm_head(hs).argmax(-1)
         out.append(tok)
     return torch.cat(out, dim=1)
+
+
+class GraphedDecoder:
+    """Greedy decode steps of a patched Llama / Qwen3 style model replayed from one CUDA graph.
+
+    The reference's decode step costs ~10 kernel launches per layer issued from Python
+    (kvcache/kitty.py:89-123, kernels/kitty_attention.py:403-526), which bounds its small-batch
+    latency.  Here the whole token (embedding, every layer with `KittyCache.step_layer`, final norm,
+    lm_head, argmax, position increment) is captured once; each later token is `plan_step()` (host
+    arithmetic + one tiny launch), one graph launch, and `finish_step()`.  The graph stays valid for
+    the life of the cache because the cache kernels read their counters from a device block.
+    """
+
+    def __init__(self, model, cache, batch: int, warmup: int = 2):
+        self.model, self.cache, self.batch = model, cache, batch
+        self.inner = model.model
+        self.h_q = model.config.get_text_config().num_attention_heads if hasattr(model.config, "get_text_config") \
+            else model.config.num_attention_heads
+        dev = next(model.parameters()).device
+        self.tok = torch.zeros((batch, 1), dtype=torch.long, device=dev)
+        self.pos = torch.zeros((1, 1), dtype=torch.long, device=dev)
+        self.graph = None
+        self.warmup = warmup
+
+    def _attention(self, attn, hidden_states, cos, sin):
+        input_shape = hidden_states.shape[:-1]
+        hidden_shape = (*input_shape, -1, attn.head_dim)
+        q = attn.q_proj(hidden_states).view(hidden_shape)
+        k = attn.k_proj(hidden_states).view(hidden_shape)
+        if getattr(attn, "q_norm", None) is not None:
+            q, k = attn.q_norm(q), attn.k_norm(k)
+        q, k = q.transpose(1, 2), k.transpose(1, 2)
+        v = attn.v_proj(hidden_states).view(hidden_shape).transpose(1, 2)
+        q, k = _rope(q, k, cos, sin)
+        out = self.cache.step_layer(attn.layer_idx, k.contiguous(), v.contiguous(), q.contiguous(), attn.scaling)
+        return attn.o_proj(out.reshape(*input_shape, -1))
+
+    def _token(self):
+        """One decode step on the static buffers: tok <- argmax(model(tok at pos)); pos += 1."""
+        m = self.inner
+        hs = m.embed_tokens(self.tok)
+        cos, sin = m.rotary_emb(hs, self.pos)
+        for layer in m.layers:
+            hs = hs + self._attention(layer.self_attn, layer.input_layernorm(hs), cos, sin)
+            hs = hs + layer.mlp(layer.post_attention_layernorm(hs))
+        nxt = self.model.lm_head(m.norm(hs)).argmax(-1)
+        self.tok.copy_(nxt)
+        self.pos.add_(1)
+
+    @torch.no_grad()
+    def step(self) -> torch.Tensor:
+        """Advance every sequence by one token.  Returns the static [B, 1] token buffer (clone it to keep it)."""
+        self.cache.plan_step(self.batch, self.h_q)
+        if self.graph is None and self.warmup > 0:
+            self.warmup -= 1                       # eager steps first: lazy initialisation must not be captured
+            self._token()
+        elif self.graph is None:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._token()
+            self.graph = g
+            g.replay()                             # capture records without running
+        else:
+            self.graph.replay()
+        self.cache.finish_step()
+        return self.tok
+
+    @torch.no_grad()
+    def generate(self, input_ids: torch.Tensor, steps: int) -> torch.Tensor:
+        """Prefill (eager, through the patched modules) and `steps` greedy tokens.  Returns [B, steps]."""
+        B, L = input_ids.shape
+        pos = torch.arange(L, device=input_ids.device).unsqueeze(0)
+        hs = self.inner(input_ids=input_ids, position_ids=pos, past_key_values=self.cache, use_cache=True,
+                        attention_mask=None).last_hidden_state
+        self.tok.copy_(self.model.lm_head(hs[:, -1:, :]).argmax(-1))
+        self.pos.fill_(L)
+        out = [self.tok.clone()]
+        for _ in range(1, steps):
+            out.append(self.step().clone())
+        return torch.cat(out, dim=1)
