@@ -52,6 +52,7 @@ def parse():
     ap.add_argument("--layers", type=int, default=32, help="decoder layers of the e2e workload")
     ap.add_argument("--graph", action="store_true", help="e2e workload: replay the decode step from a CUDA graph")
     ap.add_argument("--e2e-batch", type=int, default=16, help="batch of the e2e workload")
+    ap.add_argument("--e2e-steps", type=int, default=256, help="greedy steps of the e2e workload")
     return ap.parse_args()
 
 
@@ -275,7 +276,7 @@ def e2e_workload(args):
 
     device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(device)
-    B, L, steps = args.e2e_batch, 4096, 256
+    B, L, steps = args.e2e_batch, 4096, args.e2e_steps
     cfg = LlamaConfig(hidden_size=4096, intermediate_size=14336, num_hidden_layers=args.layers, num_attention_heads=32,
                       num_key_value_heads=8, head_dim=128, vocab_size=128256, max_position_embeddings=8192,
                       rope_theta=500000.0, tie_word_embeddings=False)
@@ -331,7 +332,7 @@ def e2e_workload(args):
                       "n_gpus": 1, "steps": steps, "ms_per_step": dec_s / (steps - 1) * 1e3, "higher_is_better": True,
                       "dtype": "bf16", "data": "synthetic",
                       "config": {"workload": f"random-init Llama-3-8B shape, {args.layers} layers, batch {B}, prompt 4096, "
-                                             "256 greedy steps, KittyCache" + (", decode steps replayed from one CUDA graph (capture included)"
+                                             f"{steps} greedy steps, KittyCache" + (", decode steps replayed from one CUDA graph (capture included)"
                                                                               if args.graph else ""), "prefill_s": pre_s, "decode_s": dec_s, "steady_ms_per_step": min(steady[1:]),
                                  "generate_s": pre_s + dec_s}}))
 
