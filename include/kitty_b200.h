@@ -182,7 +182,7 @@ typedef struct {
   kitty_counts next;     /* after the step's flushes: `before` of the next step (host use)         */
   int32_t pb, pe, ch, nchunk, has_sink, has_tail, n_slots, n_tiles, chunk_slot0, edge_slot;
   int32_t n_items, n_edge, flush_k, flush_v;
-  int32_t reserved[2];
+  int32_t edge_parts, edge_part_tok;
 } kitty_step_state;      /* 160 bytes */
 
 /* Fills *state (host memory) for one decode step of a cache whose counters are *before and, when

@@ -46,7 +46,7 @@ class KittyStepState(C.Structure):
     _fields_ = [("before", KittyCounts), ("after", KittyCounts), ("next", KittyCounts)] + \
                [(n, C.c_int32) for n in ("pb", "pe", "ch", "nchunk", "has_sink", "has_tail", "n_slots", "n_tiles",
                                          "chunk_slot0", "edge_slot", "n_items", "n_edge", "flush_k", "flush_v",
-                                         "reserved0", "reserved1")]
+                                         "edge_parts", "edge_part_tok")]
 
 
 class KittyError(RuntimeError):

@@ -29,7 +29,9 @@ struct DecodePlan {
   int32_t n_tiles;       // total tiles of the sequence (sink tile included)
   int32_t fast_chunks;   // 1: chunks are reduced by the streaming kernel, 0: by the plain kernel
   int32_t chunk_slot0;   // slot of chunk 0
-  int32_t edge_slot;     // slot written by the edge kernel (sink + tail together), when it runs
+  int32_t edge_slot;     // first slot written by the edge reduction (sink + tail), when it runs
+  int32_t edge_parts;    // the edge of one (b, h) is reduced in this many parts (slots edge_slot ...)
+  int32_t edge_part_tok; // edge tokens per part (a multiple of 64; sink tokens first, then the tail)
 };
 
 struct DecodeArgs {

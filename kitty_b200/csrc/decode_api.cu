@@ -57,6 +57,23 @@ static void plan_chunks(int n_pages, int64_t bh_gt, int grid_max, bool dynamic, 
   *nchunk_out = best_n;
 }
 
+// Edge (sink + tail) of one (b, h): in how many parts it is reduced.  With few (b, h) rows a single
+// block per row would leave most of the GPU waiting on one latency-bound reduction of up to 416 tokens,
+// so the edge is cut into 64- or 128-token parts (one work item and one partial slot each).
+constexpr int EDGE_PARTS_MAX = 7;                 // ceil((32 + 3 * 128) / 64)
+static void plan_edge(int has_sink, int has_tail, const kitty_counts &C, int64_t bh, bool split, int *parts, int *part_tok) {
+  const int ne = (has_sink ? C.Sink_Count : 0) +
+                 (has_tail ? (C.PageCount_K - C.PageCount_V) * PAGE + C.Q_Buffer_Count_K : 0);
+  int tok = 64 * EDGE_PARTS_MAX;                  // one part holds any edge
+  if (split) {
+    const int sms = sm_count();
+    if (2 * bh <= sms) tok = 64;                  // measured: pays up to about half a row per SM; beyond one row
+    else if (bh <= sms) tok = 128;                // per SM the streamed pages hide a whole edge and parts only add work
+  }
+  *part_tok = tok;
+  *parts = ne > 0 ? (ne + tok - 1) / tok : 0;
+}
+
 }  // namespace kitty
 
 using namespace kitty;
@@ -70,7 +87,7 @@ extern "C" int64_t kitty_decode_workspace_bytes(int32_t B, int32_t h_kv, int32_t
   const int64_t bh = static_cast<int64_t>(B) * h_kv;
   int cap = chunk_cap(bh, grid_max);                          // >= the cap any kernel choice uses
   cap = std::min(cap, std::max(1, (max_pages + PG_WARPS_HOST - 1) / PG_WARPS_HOST));
-  return WS_HEADER + bh * (cap + 2) * G * PART * static_cast<int64_t>(sizeof(float));
+  return WS_HEADER + bh * (cap + EDGE_PARTS_MAX) * G * PART * static_cast<int64_t>(sizeof(float));
 }
 
 extern "C" int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *counts, const void *query, int q_dtype,
@@ -116,10 +133,11 @@ extern "C" int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *c
   const int grid_max = (use_i8 ? 4 : 2) * sm_count();        // resident blocks per SM of the streaming kernel
   plan_chunks(P.pe - P.pb, static_cast<int64_t>(B) * H * n_gt, grid_max, use_i8, &P.ch, &P.nchunk);
   P.fast_chunks = (impl != 1) ? 1 : 0;
-  const int has_edge = (P.has_sink || P.has_tail) ? 1 : 0;
-  if (P.fast_chunks) {            // slots: [edge?][chunks]
-    P.n_slots = has_edge + P.nchunk;
-    P.chunk_slot0 = has_edge;
+  plan_edge(P.has_sink, P.has_tail, C, static_cast<int64_t>(B) * H, P.fast_chunks != 0, &P.edge_parts, &P.edge_part_tok);
+  const int has_edge = P.edge_parts > 0 ? 1 : 0;
+  if (P.fast_chunks) {            // slots: [edge parts][chunks]
+    P.n_slots = P.edge_parts + P.nchunk;
+    P.chunk_slot0 = P.edge_parts;
     P.edge_slot = 0;
   } else {                        // slots: [sink?][chunks][tail?]
     P.n_slots = P.has_sink + P.nchunk + P.has_tail;
@@ -141,7 +159,7 @@ extern "C" int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *c
   if (use_i8) {
     // the int8 streaming kernel also reduces the edge (sink + tail) inside its own grid
     const int64_t items = static_cast<int64_t>(B) * H * P.nchunk;
-    const int64_t n_edge = has_edge ? static_cast<int64_t>(B) * H : 0;
+    const int64_t n_edge = static_cast<int64_t>(B) * H * P.edge_parts;
     if (items + n_edge > 0) {
       const int grid = static_cast<int>(std::min<int64_t>(items + n_edge, grid_max));
       if (int rc = launch_decode_paged_i8(a, static_cast<int>(items), static_cast<int>(n_edge), grid, s)) return rc;
@@ -262,12 +280,12 @@ extern "C" int kitty_plan_step(const kitty_layer *layer, const kitty_counts *bef
   st.has_tail = (st.n_tiles - 1 - pv) > 0 ? 1 : 0;
   const int grid_max = 4 * sm_count();
   plan_chunks(pv, static_cast<int64_t>(B) * H, grid_max, true, &st.ch, &st.nchunk);
-  const int has_edge = (st.has_sink || st.has_tail) ? 1 : 0;
-  st.n_slots = has_edge + st.nchunk;
-  st.chunk_slot0 = has_edge;
+  plan_edge(st.has_sink, st.has_tail, c, static_cast<int64_t>(B) * H, true, &st.edge_parts, &st.edge_part_tok);
+  st.n_slots = st.edge_parts + st.nchunk;
+  st.chunk_slot0 = st.edge_parts;
   st.edge_slot = 0;
   st.n_items = B * H * st.nchunk;
-  st.n_edge = has_edge ? B * H : 0;
+  st.n_edge = B * H * st.edge_parts;
   if (device_state != nullptr) {
     if ((reinterpret_cast<uintptr_t>(device_state) & 15u) != 0) return KITTY_E_BADARG;
     store_step_state_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(st, device_state);

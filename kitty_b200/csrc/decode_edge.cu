@@ -10,7 +10,7 @@ template <int NG>
 __global__ void __launch_bounds__(EDGE_KERNEL_WARPS * 32) decode_edge_kernel(DecodeArgs a) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   EdgeSmem<EDGE_KERNEL_WARPS> &sm = *reinterpret_cast<EdgeSmem<EDGE_KERNEL_WARPS> *>(smem_raw);
-  edge_item<NG, EDGE_KERNEL_WARPS>(a, a.P, a.C, sm, blockIdx.y, blockIdx.x);
+  edge_item<NG, EDGE_KERNEL_WARPS>(a, a.P, a.C, sm, blockIdx.y, blockIdx.x, blockIdx.z);
 }
 
 int launch_decode_edge(const DecodeArgs &a, cudaStream_t s) {
@@ -25,7 +25,7 @@ int launch_decode_edge(const DecodeArgs &a, cudaStream_t s) {
       return KITTY_E_CUDA;
     configured = dev;
   }
-  dim3 grid(a.P.H, a.P.B);
+  dim3 grid(a.P.H, a.P.B, a.P.edge_parts);
   if (a.P.G <= 4) decode_edge_kernel<4><<<grid, EDGE_KERNEL_WARPS * 32, smem, s>>>(a);
   else if (a.P.G <= 8) decode_edge_kernel<8><<<grid, EDGE_KERNEL_WARPS * 32, smem, s>>>(a);
   else decode_edge_kernel<16><<<grid, EDGE_KERNEL_WARPS * 32, smem, s>>>(a);

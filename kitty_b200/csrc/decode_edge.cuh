@@ -33,11 +33,15 @@ struct EdgeSmem {
   uint8_t inv[NW][DB];
 };
 
-// Reduces the edge of one (batch b, kv-head h) with the NW warps of the calling block and writes the
-// partial into the workspace slot P.edge_slot.  Every thread of the block must call it.
+// Reduces part `part` of the edge of one (batch b, kv-head h) with the NW warps of the calling block and
+// writes the partial into the workspace slot P.edge_slot + part.  The edge tokens are numbered sink first,
+// then the tail; part i covers tokens [i * P.edge_part_tok, (i + 1) * P.edge_part_tok).  Part boundaries are
+// multiples of 64 and the tail starts at token 0 or 32, so a 16-token key tile is never split.  With few
+// (b, h) rows the host asks for several small parts so that the latency-bound edge spreads over more blocks.
+// Every thread of the block must call it.
 template <int NG, int NW>
 __device__ __forceinline__ void edge_item(const DecodeArgs &a, const DecodePlan &P, const kitty_counts &C,
-                                          EdgeSmem<NW> &sm, int b, int h) {
+                                          EdgeSmem<NW> &sm, int b, int h, int part) {
   constexpr int EDGE_WARPS = NW;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
   const int H = P.H, G = P.G;
@@ -48,7 +52,9 @@ __device__ __forceinline__ void edge_item(const DecodeArgs &a, const DecodePlan 
   const int npk = P.has_tail ? (C.PageCount_K - C.PageCount_V) : 0;     // key pages without a packed value page
   const int qk_n = P.has_tail ? C.Q_Buffer_Count_K : 0;
   const int tail_n = npk * PAGE + qk_n;
-  const int ne = sink_n + tail_n;
+  const int ne_all = sink_n + tail_n;
+  const int lo = part * P.edge_part_tok;                       // this part: edge tokens [lo, ne)
+  const int ne = min(ne_all, lo + P.edge_part_tok);
 
   // ---- stage the query and the tail's packed key pages ---- //
   for (int i = tid; i < n_gt * 8 * HD; i += EDGE_WARPS * 32) {
@@ -59,6 +65,7 @@ __device__ __forceinline__ void edge_item(const DecodeArgs &a, const DecodePlan 
   }
   if (tid < EDGE_WARPS * DB) sm.inv[tid / DB][tid % DB] = 0;
   for (int p = 0; p < npk; ++p) {
+    if (sink_n + p * PAGE >= ne || sink_n + (p + 1) * PAGE <= lo) continue;     // page outside this part
     const int64_t pid = a.L.PageTable_K[static_cast<int64_t>(b) * a.L.max_page + C.PageCount_V + p];
     const uint4 *src = reinterpret_cast<const uint4 *>(a.L.KeyCache + pid * (static_cast<int64_t>(H) * K_HEAD) + h * K_HEAD);
     for (int i = tid; i < K_HEAD / 16; i += EDGE_WARPS * 32) reinterpret_cast<uint4 *>(sm.krec[p])[i] = src[i];
@@ -68,7 +75,7 @@ __device__ __forceinline__ void edge_item(const DecodeArgs &a, const DecodePlan 
   __syncthreads();
 
   // ---- 1a. packed key pages of the tail: one (page, group of 8 heads) per warp ---- //
-  if (warp < npk * n_gt) {
+  if (warp < npk * n_gt && sink_n + (warp / n_gt) * PAGE < ne && sink_n + (warp / n_gt + 1) * PAGE > lo) {
     const int p = warp / n_gt, gt = warp % n_gt;
     uint32_t q2[8][2];
     load_q_frags(&sm.qs[gt * 8], gid, tig, q2);
@@ -96,6 +103,7 @@ __device__ __forceinline__ void edge_item(const DecodeArgs &a, const DecodePlan 
         base = static_cast<const __half *>(a.L.Q_Buffer_K) + bh * PAGE * HD;
         row0 = 16 * (j - ns_t); nrows = qk_n; e0 = sink_n + npk * PAGE + row0;
       }
+      if (e0 < lo || e0 >= ne) continue;                        // tile outside this part (warp-uniform)
       // lane (gid, tig): rows row0+gid and row0+gid+8, channels [32*tig, 32*tig+32)
       uint4 ra[4], rb[4];
       const int rA = row0 + gid, rB = row0 + gid + 8;
@@ -130,11 +138,11 @@ __device__ __forceinline__ void edge_item(const DecodeArgs &a, const DecodePlan 
   // ---- 2. softmax statistics per query head; probabilities replace the logits ---- //
   for (int g = warp; g < G; g += EDGE_WARPS) {
     float mx = -INFINITY;
-    for (int e = lane; e < ne; e += 32) mx = fmaxf(mx, sm.S[g][e]);
+    for (int e = lo + lane; e < ne; e += 32) mx = fmaxf(mx, sm.S[g][e]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     float s = 0.f;
-    for (int e = lane; e < ne; e += 32) {
+    for (int e = lo + lane; e < ne; e += 32) {
       const float p = ex2(sm.S[g][e] - mx);
       sm.S[g][e] = p;
       s += p;
@@ -162,7 +170,7 @@ __device__ __forceinline__ void edge_item(const DecodeArgs &a, const DecodePlan 
     return ringv + ((r - C.Q_Buffer_Count_V + C.Write_Offset_Local_V) & (PAGE - 1)) * HD;
   };
   constexpr int UNR = 16;
-  for (int e0 = warp; e0 < ne; e0 += UNR * EDGE_WARPS) {
+  for (int e0 = lo + warp; e0 < ne; e0 += UNR * EDGE_WARPS) {
     uint2 raw[UNR];
 #pragma unroll
     for (int u = 0; u < UNR; ++u) {
@@ -203,12 +211,12 @@ __device__ __forceinline__ void edge_item(const DecodeArgs &a, const DecodePlan 
   }
 
   // ---- 4. partial result ---- //
-  float *dst = a.partials + ((bh * P.n_slots + P.edge_slot) * G) * PART;
+  float *dst = a.partials + ((bh * P.n_slots + P.edge_slot + part) * G) * PART;
   if (tid < HD)
     for (int g = 0; g < G; ++g) dst[g * PART + tid] = sm.red[g][tid];
   if (tid < G) {
-    dst[tid * PART + HD] = (ne > 0) ? sm.mx[tid] : -INFINITY;
-    dst[tid * PART + HD + 1] = (ne > 0) ? sm.sum[tid] : 0.f;
+    dst[tid * PART + HD] = (ne > lo) ? sm.mx[tid] : -INFINITY;
+    dst[tid * PART + HD + 1] = (ne > lo) ? sm.sum[tid] : 0.f;
   }
 }
 

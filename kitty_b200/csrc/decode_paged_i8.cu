@@ -168,6 +168,7 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
     DecodePlan p = a.P;
     p.pb = d.pb; p.pe = d.pe; p.ch = d.ch; p.nchunk = d.nchunk; p.has_sink = d.has_sink; p.has_tail = d.has_tail;
     p.n_slots = d.n_slots; p.n_tiles = d.n_tiles; p.chunk_slot0 = d.chunk_slot0; p.edge_slot = d.edge_slot;
+    p.edge_parts = d.edge_parts; p.edge_part_tok = d.edge_part_tok;
     smem.dyn_plan = p;
     smem.dyn_counts = d.after;
     smem.dyn_items = d.n_items;
@@ -215,9 +216,9 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
     const int e_after = static_cast<int>((static_cast<long long>(it) + 1) * n_edge / total);
     const int item = it - e_before;        // index among the page-pair items
     if (e_after > e_before) {
-      // ---- edge item: sink + tail of one (batch, kv-head), by the whole block ---- //
-      const int ebh = e_before;
-      edge_item<4, I8_WARPS>(a, P, C, smem.u.e, ebh / H, ebh % H);
+      // ---- edge item: one part of the sink + tail of one (batch, kv-head), by the whole block ---- //
+      const int ebh = e_before / P.edge_parts, part = e_before % P.edge_parts;
+      edge_item<4, I8_WARPS>(a, P, C, smem.u.e, ebh / H, ebh % H, part);
       __syncthreads();
       ws.inv[lane] = 0;  // the slot table was overwritten: keep its entries valid positions
       continue;
