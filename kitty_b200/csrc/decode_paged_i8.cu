@@ -11,12 +11,14 @@
 // The 10368 bytes of a page pair are fetched from HBM exactly once.
 //
 // Arithmetic: mma.sync.m16n8k32 on 8-bit integers.
-//  * A operand = the packed codes themselves.  Four words of the record (four
-//    channels x 16 tokens for keys, four tokens x 16 channels for values) are
-//    byte-transposed with 8 PRMT so that a register holds the same byte of four
-//    contraction indices; `reg & (0x03030303 << 2r)` is then an A register: the
-//    u8 values code * 4^r of one token (channel) for four contraction indices —
-//    four fields per logic instruction, no shifts.
+//  * A operand = the packed codes themselves.  A record is a matrix of 32-byte
+//    rows (one row per channel for keys, per token for values) whose bytes hold 4
+//    fields.  `ldmatrix.m16n16.x2.trans.b8` reads 32 rows x 16 byte columns
+//    transposed and hands every lane exactly the A fragment of m16n8k32 (rows =
+//    byte columns, contraction index = record row); `reg & (0x03030303 << 2r)` is
+//    then the u8 operand code * 4^r of field r — four fields per logic
+//    instruction, no shifts and no byte permutes.  Tile (half hf, field r) row m
+//    is token (or channel) 64*hf + 4*m + r.
 //  * B operand = the small vector (q*scale for keys, p*scale for values) in
 //    16-bit fixed point, split into a high and a low 8-bit limb.  The 8 columns
 //    of the tile are (head, limb) for 4 heads, so one mma covers both limbs and
@@ -25,8 +27,7 @@
 //    fixed-point scale.  Conversion to fixed point is a fused multiply-add with
 //    the magic constant 1.5*2^23 (the integer lands in the mantissa).
 //  * The rank-1 terms (sum q*min, sum p*zero, sum p) are a few fp32 FMAs per lane.
-// Per page pair and warp: 72 mma.sync and roughly 1000 other instructions, about
-// 600 of them on the integer/logic pipe.
+// Per page pair and warp: 72 mma.sync, 18 ldmatrix and roughly 800 other instructions.
 //
 // Every wait on an mbarrier is bounded; when one runs out the warp sets the
 // workspace's status word, stops consuming and the call's result is invalid.
@@ -49,22 +50,19 @@ constexpr float VFIX = 60000.0f;    // p * scale' <= VFIX < 2^16 (unsigned limbs
 constexpr float MAGIC_S = 12582912.0f;   // 1.5 * 2^23: signed integers in the low mantissa bits
 constexpr float MAGIC_U = 8388608.0f;    // 2^23: unsigned integers in the low mantissa bits
 
-// Per-channel / per-token arrays are kept in "arranged" order so that the 8
-// values one lane needs for a k-step are contiguous:
-//   position(c) = (c >> 5) * 32 + (c & 3) * 8 + ((c >> 4) & 1) * 4 + ((c >> 2) & 3)
-// i.e. k-step ks, thread-in-group tg reads positions ks*32 + tg*8 + {0..3} (contraction bytes
-// 4*tg + i  <->  index 32*ks + tg + 4*i) and + {4..7} (bytes 16 + 4*tg + i  <->  32*ks + 16 + tg + 4*i).
+// The contraction index of a k-step is the record row itself: bytes 4*tg + i of the B registers
+// <-> rows 32*ks + 4*tg + i (b0) and 32*ks + 16 + 4*tg + i (b1).
 struct I8Warp {
   __align__(128) uint8_t stage[I8_STAGE_BYTES];
-  __align__(16) float sarr[HD];        // keys: scale' per channel (arranged); values: scale' per token (plain)
-  __align__(16) float marr[HD];        // keys: min per channel (arranged);    values: zero-point per token (plain)
-  __align__(16) uint32_t pb[8 * PB_RS]; // probabilities * scale' as limb bytes: [head*2 + limb][k-step][quad][tg] words
-  uint8_t inv[DB];                     // slot -> arranged position of its channel
+  __align__(16) float sarr[HD];        // keys: scale' per channel; values: scale' per token
+  __align__(16) float marr[HD];        // keys: min per channel;    values: zero-point per token
+  __align__(16) uint32_t pb[8 * PB_RS]; // probabilities * scale' as limb bytes: [head*2 + limb][token / 4] words
+  uint8_t inv[DB];                     // slot -> its channel
 };
 
 struct I8Main {
   I8Warp w[I8_WARPS];
-  __align__(16) float qarr[4][QROW];   // query / qmax per head, arranged
+  __align__(16) float qarr[4][QROW];   // query / qmax per head
   float qmax[4];
 };
 
@@ -100,16 +98,6 @@ __device__ __forceinline__ void imma_u8u8(int (&c)[4], uint32_t a0, uint32_t a1,
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// 4x4 byte transpose: t[j] = (w0.byte j, w1.byte j, w2.byte j, w3.byte j).
-__device__ __forceinline__ void transpose4(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, uint32_t (&t)[4]) {
-  const uint32_t lo01 = __byte_perm(w0, w1, 0x5140), hi01 = __byte_perm(w0, w1, 0x7362);
-  const uint32_t lo23 = __byte_perm(w2, w3, 0x5140), hi23 = __byte_perm(w2, w3, 0x7362);
-  t[0] = __byte_perm(lo01, lo23, 0x5410);
-  t[1] = __byte_perm(lo01, lo23, 0x7632);
-  t[2] = __byte_perm(hi01, hi23, 0x5410);
-  t[3] = __byte_perm(hi01, hi23, 0x7632);
-}
-
 // Four fixed-point values -> one B register holding their limb bytes.  sel picks the byte
 // (0x0040: byte 0 of both sources, 0x0051: byte 1 of both sources).
 __device__ __forceinline__ uint32_t pack_limb(float y0, float y1, float y2, float y3, uint32_t sel) {
@@ -118,27 +106,24 @@ __device__ __forceinline__ uint32_t pack_limb(float y0, float y1, float y2, floa
   return __byte_perm(p01, p23, 0x5410);
 }
 
-// One k-step of 32 contraction indices against 128 rows, rows = 16*gid + {0..15} of each lane.
-// words: base of the record's 32-bit words; the word of contraction index x and row group gid
-// is words[x * 8 + gid].  idx0: first contraction index of the k-step; stride between the four
-// bytes of a quad is `step` indices.  Tiles mu = 4*jj + r: row gid <-> 16*gid + 4*jj + r,
-// row gid + 8 <-> 16*gid + 8 + 4*jj + r, weight 4^r.
+// One k-step of 32 contraction indices (record rows k0 .. k0+31) against the 128 byte-column x field rows.
+// row_addr: shared-memory address of row k0 + lane of the record (32 bytes per row).  Tile 4*hf + r:
+// fragment row m (gid, gid + 8) <-> byte column 16*hf + m, field r <-> index 64*hf + 4*m + r, weight 4^r.
 template <bool kSignedB>
-__device__ __forceinline__ void kstep32(const uint32_t *words, int gid, int idxA, int idxB, int step, uint32_t b0,
-                                        uint32_t b1, int (&c)[8][4]) {
-  uint32_t ta[4], tb[4];
-  transpose4(words[(idxA)*8 + gid], words[(idxA + step) * 8 + gid], words[(idxA + 2 * step) * 8 + gid],
-             words[(idxA + 3 * step) * 8 + gid], ta);
-  transpose4(words[(idxB)*8 + gid], words[(idxB + step) * 8 + gid], words[(idxB + 2 * step) * 8 + gid],
-             words[(idxB + 3 * step) * 8 + gid], tb);
+__device__ __forceinline__ void kstep32(uint32_t row_addr, uint32_t b0, uint32_t b1, int (&c)[8][4]) {
 #pragma unroll
-  for (int jj = 0; jj < 2; ++jj)
+  for (int hf = 0; hf < 2; ++hf) {
+    uint32_t a0, a1, a2, a3;
+    asm volatile("ldmatrix.sync.aligned.m16n16.x2.trans.shared.b8 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3)
+                 : "r"(row_addr + 16 * hf));
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
       const uint32_t msk = 0x03030303u << (2 * r);
-      if (kSignedB) imma_u8s8(c[4 * jj + r], ta[jj] & msk, ta[jj + 2] & msk, tb[jj] & msk, tb[jj + 2] & msk, b0, b1);
-      else imma_u8u8(c[4 * jj + r], ta[jj] & msk, ta[jj + 2] & msk, tb[jj] & msk, tb[jj + 2] & msk, b0, b1);
+      if (kSignedB) imma_u8s8(c[4 * hf + r], a0 & msk, a1 & msk, a2 & msk, a3 & msk, b0, b1);
+      else imma_u8u8(c[4 * hf + r], a0 & msk, a1 & msk, a2 & msk, a3 & msk, b0, b1);
     }
+  }
 }
 
 __device__ __forceinline__ void i8_issue_k(const DecodeArgs &a, int b, int h, int page, uint32_t dst, uint32_t bar) {
@@ -229,7 +214,7 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
     const int p0 = P.pb + c * P.ch;
     const int p1 = min(P.pe, p0 + P.ch);
 
-    // ---- query of head `warp`: maximum, then q / qmax in arranged order ---- //
+    // ---- query of head `warp`: maximum, then q / qmax ---- //
     {
       float qv[4], mx = 0.f;
 #pragma unroll
@@ -242,9 +227,8 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
       for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
       mx = fmaxf(mx, 1e-30f);
       const float inv_mx = 1.0f / mx;
-      const int base = ((lane >> 3) << 5) + (lane & 7);          // arranged position of channel 4*lane + i is base + 8*i
-#pragma unroll
-      for (int i = 0; i < 4; ++i) sm.qarr[warp][base + 8 * i] = qv[i] * inv_mx;
+      *reinterpret_cast<float4 *>(&sm.qarr[warp][4 * lane]) =
+          make_float4(qv[0] * inv_mx, qv[1] * inv_mx, qv[2] * inv_mx, qv[3] * inv_mx);
       if (lane == 0) sm.qmax[warp] = mx;
     }
     // this warp's pages: p0 + warp, p0 + warp + I8_WARPS, ...
@@ -262,10 +246,10 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
 
     // This lane's output head is `tig` (accumulator columns 2*tig, 2*tig+1 = its high and low limb).
     const float qmax_t = sm.qmax[tig];
-    float acc[8][2];       // out[channel 16*gid + 4*jj + r (+8)][head tig], tile mu = 4*jj + r
+    float acc[8][2];       // out[channel 64*hf + 4*gid + r (+32)][head tig], tile 4*hf + r
 #pragma unroll
     for (int m = 0; m < 8; ++m) acc[m][0] = acc[m][1] = 0.f;
-    float zsum = 0.f, lsum = 0.f;      // this lane's share of sum p*zero-point and sum p (tokens 16*gid..16*gid+15, head tig)
+    float zsum = 0.f, lsum = 0.f;      // this lane's share of sum p*zero-point and sum p (its 16 tokens, head tig)
     float m_run = -INFINITY;
 
     for (int pg = first; pg < p1 && !dead; pg += I8_WARPS) {
@@ -274,28 +258,22 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
       if (!mbar_wait(bar_k, parity)) { dead = true; break; }
       inflight &= ~1u;
       const uint8_t *stg = ws.stage;
-      const uint32_t *kw = reinterpret_cast<const uint32_t *>(stg + I8_OFF_KREC);
-      const uint32_t *hw = reinterpret_cast<const uint32_t *>(stg + I8_OFF_KREC + K_OFF_HI);
       const uint32_t *km = reinterpret_cast<const uint32_t *>(stg + I8_OFF_KMETA);
-      const uint32_t *vw = reinterpret_cast<const uint32_t *>(stg + I8_OFF_VREC);
       const uint32_t *vm = reinterpret_cast<const uint32_t *>(stg + I8_OFF_VMETA);
 
-      // ---- key pre-pass: slot table, scale' = scale * KFIX / max scale and min, arranged ---- //
+      // ---- key pre-pass: slot table, scale' = scale * KFIX / max scale and min ---- //
       float k_unit;      // value of one fixed-point unit of q^ * scale
       {
         const uint32_t w = *reinterpret_cast<const uint32_t *>(stg + I8_OFF_KREC + K_OFF_IDX + 4 * lane);
-        const int base = ((lane >> 3) << 5) + (lane & 7);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const uint32_t s = (w >> (8 * i)) & 0xffu;
-          if (s < DB) ws.inv[s] = static_cast<uint8_t>(base + 8 * i);
+          if (s < DB) ws.inv[s] = static_cast<uint8_t>(4 * lane + i);
         }
-        // arranged positions 4*lane .. 4*lane+3  <->  channels 32*ks + 16*quad + tg + 4*i
-        const int ch0 = ((lane >> 3) << 5) + ((lane & 1) << 4) + ((lane >> 1) & 3);
         float sc[4], mn[4], smax = 0.f;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&km[ch0 + 4 * i]));
+          const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&km[4 * lane + i]));
           sc[i] = f.x;
           mn[i] = f.y;
           smax = fmaxf(smax, f.x);
@@ -316,14 +294,14 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
       const float *qrow = sm.qarr[colhead];
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks) {
-        const int pos = ks * 32 + tig * 8;
-        const float4 qa = *reinterpret_cast<const float4 *>(qrow + pos), qb = *reinterpret_cast<const float4 *>(qrow + pos + 4);
-        const float4 sa = *reinterpret_cast<const float4 *>(&ws.sarr[pos]), sb = *reinterpret_cast<const float4 *>(&ws.sarr[pos + 4]);
+        const int pos = ks * 32 + tig * 4;
+        const float4 qa = *reinterpret_cast<const float4 *>(qrow + pos), qb = *reinterpret_cast<const float4 *>(qrow + pos + 16);
+        const float4 sa = *reinterpret_cast<const float4 *>(&ws.sarr[pos]), sb = *reinterpret_cast<const float4 *>(&ws.sarr[pos + 16]);
         const uint32_t b0 = pack_limb(fmaf(qa.x, sa.x, kmagic), fmaf(qa.y, sa.y, kmagic), fmaf(qa.z, sa.z, kmagic),
                                       fmaf(qa.w, sa.w, kmagic), limb_sel);
         const uint32_t b1 = pack_limb(fmaf(qb.x, sb.x, kmagic), fmaf(qb.y, sb.y, kmagic), fmaf(qb.z, sb.z, kmagic),
                                       fmaf(qb.w, sb.w, kmagic), limb_sel);
-        kstep32<true>(kw, gid, 32 * ks + tig, 32 * ks + 16 + tig, 4, b0, b1, cl);
+        kstep32<true>(stage_u32 + I8_OFF_KREC + (32 * ks + lane) * 32, b0, b1, cl);
       }
       // high plane: 32 slots = one k-step; bytes 4*tig + i <-> slot 4*tig + i, bytes 16 + 4*tig + i <-> slot 16 + 4*tig + i;
       // operand = 4 * q^ * scale' of the slot's channel
@@ -339,14 +317,14 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
         }
         const uint32_t b0 = pack_limb(ya[0], ya[1], ya[2], ya[3], limb_sel);
         const uint32_t b1 = pack_limb(yb[0], yb[1], yb[2], yb[3], limb_sel);
-        kstep32<true>(hw, gid, 4 * tig, 16 + 4 * tig, 1, b0, b1, cl);
+        kstep32<true>(stage_u32 + I8_OFF_KREC + K_OFF_HI + lane * 32, b0, b1, cl);
       }
       __syncwarp();      // every lane is done with the key part: request the next page's
       if (nxt < p1) {
         if (lane == 0) i8_issue_k(a, b, h, nxt, stage_u32, bar_k);
         inflight |= 1u;
       }
-      // sum_c q*min for head tig: this lane covers arranged positions 16*gid .. 16*gid+15
+      // sum_c q*min for head tig: this lane covers channels 16*gid .. 16*gid+15
       float bias = 0.f;
       {
         const float *qt = sm.qarr[tig] + 16 * gid;
@@ -386,8 +364,8 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
         *reinterpret_cast<float4 *>(&ws.marr[4 * lane]) = make_float4(zp[0], zp[1], zp[2], zp[3]);
       }
 
-      // ================= online softmax: 16 tokens (16*gid + e) of head tig per lane ================= //
-      // e = 8*h8 + 4*jj + r  <->  cl[4*jj + r][2*h8 (hi), 2*h8 + 1 (lo)]
+      // ================= online softmax: 16 tokens of head tig per lane ================= //
+      // e = 8*h8 + 4*hf + r  <->  cl[4*hf + r][2*h8 (hi), 2*h8 + 1 (lo)]  <->  token 64*hf + 32*h8 + 4*gid + r
       float lg[16];
       {
         const float u0 = k_unit * qmax_t;
@@ -420,45 +398,42 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
       }
       __syncwarp();      // value scales / zero-points visible
       {
-        float y[16];
+        // four consecutive tokens 64*hf + 32*h8 + 4*gid + {0..3} are one B word (k-step 2*hf + h8, word gid)
+        uint32_t *dst = ws.pb + (2 * tig) * PB_RS + gid;
 #pragma unroll
-        for (int v4 = 0; v4 < 4; ++v4) {
-          const float4 s4 = *reinterpret_cast<const float4 *>(&ws.sarr[16 * gid + 4 * v4]);
-          const float4 z4 = *reinterpret_cast<const float4 *>(&ws.marr[16 * gid + 4 * v4]);
-          const float sv[4] = {s4.x, s4.y, s4.z, s4.w}, zv[4] = {z4.x, z4.y, z4.z, z4.w};
+        for (int hf = 0; hf < 2; ++hf)
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float p = ex2(lg[4 * v4 + i] - m_run);
-            lsum += p;
-            zsum = fmaf(p, zv[i], zsum);
-            y[4 * v4 + i] = fmaf(p, sv[i], MAGIC_U);
+          for (int h8 = 0; h8 < 2; ++h8) {
+            const int t0 = 64 * hf + 32 * h8 + 4 * gid;
+            const float4 s4 = *reinterpret_cast<const float4 *>(&ws.sarr[t0]);
+            const float4 z4 = *reinterpret_cast<const float4 *>(&ws.marr[t0]);
+            const float sv[4] = {s4.x, s4.y, s4.z, s4.w}, zv[4] = {z4.x, z4.y, z4.z, z4.w};
+            float y[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+              const float p = ex2(lg[8 * h8 + 4 * hf + r] - m_run);
+              lsum += p;
+              zsum = fmaf(p, zv[r], zsum);
+              y[r] = fmaf(p, sv[r], MAGIC_U);
+            }
+            // both limbs from one pair of PRMTs: (a.b0, b.b0, a.b1, b.b1)
+            const uint32_t pab = __byte_perm(__float_as_uint(y[0]), __float_as_uint(y[1]), 0x5140);
+            const uint32_t pcd = __byte_perm(__float_as_uint(y[2]), __float_as_uint(y[3]), 0x5140);
+            dst[(2 * hf + h8) * 8] = __byte_perm(pab, pcd, 0x7632);               // high limbs
+            dst[PB_RS + (2 * hf + h8) * 8] = __byte_perm(pab, pcd, 0x5410);       // low limbs
           }
-        }
-        // limb bytes: word tg of limb block = tokens e = tg + 4*i (i = 0..3); both limbs from one pair of PRMTs
-        uint32_t whi[4], wlo[4];
-#pragma unroll
-        for (int tg = 0; tg < 4; ++tg) {
-          const uint32_t pab = __byte_perm(__float_as_uint(y[tg]), __float_as_uint(y[tg + 4]), 0x5140);        // (a.b0, b.b0, a.b1, b.b1)
-          const uint32_t pcd = __byte_perm(__float_as_uint(y[tg + 8]), __float_as_uint(y[tg + 12]), 0x5140);
-          wlo[tg] = __byte_perm(pab, pcd, 0x5410);
-          whi[tg] = __byte_perm(pab, pcd, 0x7632);
-        }
-        // pb word index = (head*2 + limb)*PB_RS + ks*8 + quad*4 + tg, tokens 16*gid.. <-> ks = gid >> 1, quad = gid & 1
-        uint32_t *dst = ws.pb + (2 * tig) * PB_RS + (gid >> 1) * 8 + (gid & 1) * 4;
-        *reinterpret_cast<uint4 *>(dst) = make_uint4(whi[0], whi[1], whi[2], whi[3]);
-        *reinterpret_cast<uint4 *>(dst + PB_RS) = make_uint4(wlo[0], wlo[1], wlo[2], wlo[3]);
       }
       __syncwarp();
 
       // ================= P V ================= //
-      // rows = channels 16*gid + {0..15}; contraction bytes 4*tig + i <-> token 32*ks + tig + 4*i, 16 + 4*tig + i <-> +16
+      // rows = channels; contraction bytes 4*tig + i <-> token 32*ks + 4*tig + i (b0), 32*ks + 16 + 4*tig + i (b1)
       int cv[8][4];
 #pragma unroll
       for (int m = 0; m < 8; ++m) cv[m][0] = cv[m][1] = cv[m][2] = cv[m][3] = 0;
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks) {
         const uint32_t b0 = ws.pb[gid * PB_RS + ks * 8 + tig], b1 = ws.pb[gid * PB_RS + ks * 8 + 4 + tig];
-        kstep32<false>(vw, gid, 32 * ks + tig, 32 * ks + 16 + tig, 4, b0, b1, cv);
+        kstep32<false>(stage_u32 + I8_OFF_VREC + (32 * ks + lane) * 32, b0, b1, cv);
       }
       {
         const float u0 = v_unit;
@@ -503,8 +478,8 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
       for (int jj = 0; jj < 2; ++jj)
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
-          w[16 * gid + 4 * jj + r] = acc[4 * jj + r][0] + zsum;
-          w[16 * gid + 8 + 4 * jj + r] = acc[4 * jj + r][1] + zsum;
+          w[64 * jj + 4 * gid + r] = acc[4 * jj + r][0] + zsum;
+          w[64 * jj + 32 + 4 * gid + r] = acc[4 * jj + r][1] + zsum;
         }
       if (gid == 0) {
         w[HD] = m_run;
