@@ -126,16 +126,16 @@ __device__ __forceinline__ void kstep32(uint32_t row_addr, uint32_t b0, uint32_t
   }
 }
 
-__device__ __forceinline__ void i8_issue_k(const DecodeArgs &a, int b, int h, int page, uint32_t dst, uint32_t bar) {
+// pk / pv: the page's row in the cache (page-table entry), read by the caller well before the copy is
+// issued so that the table lookup does not stall the warp.
+__device__ __forceinline__ void i8_issue_k(const DecodeArgs &a, int h, int64_t pk, uint32_t dst, uint32_t bar) {
   const int H = a.P.H;
-  const int64_t pk = a.L.PageTable_K[static_cast<int64_t>(b) * a.L.max_page + page];
   mbar_expect_tx(bar, I8_KPART);
   bulk_g2s(dst + I8_OFF_KREC, a.L.KeyCache + pk * (static_cast<int64_t>(H) * K_HEAD) + static_cast<int64_t>(h) * K_HEAD, K_HEAD, bar);
   bulk_g2s(dst + I8_OFF_KMETA, static_cast<const uint8_t *>(a.L.KeyCache_metadata) + (pk * H + h) * META_HEAD, META_HEAD, bar);
 }
-__device__ __forceinline__ void i8_issue_v(const DecodeArgs &a, int b, int h, int page, uint32_t dst, uint32_t bar) {
+__device__ __forceinline__ void i8_issue_v(const DecodeArgs &a, int h, int64_t pv, uint32_t dst, uint32_t bar) {
   const int H = a.P.H;
-  const int64_t pv = a.L.PageTable_V[static_cast<int64_t>(b) * a.L.max_page + page];
   mbar_expect_tx(bar, I8_VPART);
   bulk_g2s(dst + I8_OFF_VREC, a.L.ValueCache + pv * (static_cast<int64_t>(H) * V_HEAD) + static_cast<int64_t>(h) * V_HEAD, V_HEAD, bar);
   bulk_g2s(dst + I8_OFF_VMETA, static_cast<const uint8_t *>(a.L.ValueCache_metadata) + (pv * H + h) * META_HEAD, META_HEAD, bar);
@@ -237,8 +237,8 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
       if (lane == 0) {
         // the stage may have been written through the generic proxy (merge buffer): order that before the bulk copies
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        i8_issue_k(a, b, h, first, stage_u32, bar_k);
-        i8_issue_v(a, b, h, first, stage_u32, bar_v);
+        i8_issue_k(a, h, a.L.PageTable_K[static_cast<int64_t>(b) * a.L.max_page + first], stage_u32, bar_k);
+        i8_issue_v(a, h, a.L.PageTable_V[static_cast<int64_t>(b) * a.L.max_page + first], stage_u32, bar_v);
       }
       inflight = 3u;
     }
@@ -255,6 +255,12 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
     for (int pg = first; pg < p1 && !dead; pg += I8_WARPS) {
       const uint32_t parity = seq & 1u;
       const int nxt = pg + I8_WARPS;
+      // page-table entries of the next page: requested now, used after Q K^T / P V
+      uint32_t pk_nxt = 0, pv_nxt = 0;
+      if (nxt < p1) {
+        pk_nxt = static_cast<uint32_t>(a.L.PageTable_K[static_cast<int64_t>(b) * a.L.max_page + nxt]);
+        pv_nxt = static_cast<uint32_t>(a.L.PageTable_V[static_cast<int64_t>(b) * a.L.max_page + nxt]);
+      }
       if (!mbar_wait(bar_k, parity)) { dead = true; break; }
       inflight &= ~1u;
       const uint8_t *stg = ws.stage;
@@ -321,7 +327,7 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
       }
       __syncwarp();      // every lane is done with the key part: request the next page's
       if (nxt < p1) {
-        if (lane == 0) i8_issue_k(a, b, h, nxt, stage_u32, bar_k);
+        if (lane == 0) i8_issue_k(a, h, pk_nxt, stage_u32, bar_k);
         inflight |= 1u;
       }
       // sum_c q*min for head tig: this lane covers channels 16*gid .. 16*gid+15
@@ -450,7 +456,7 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
       __syncwarp();      // every lane is done with the value part and with the warp's buffers
       ++seq;
       if (nxt < p1) {
-        if (lane == 0) i8_issue_v(a, b, h, nxt, stage_u32, bar_v);
+        if (lane == 0) i8_issue_v(a, h, pv_nxt, stage_u32, bar_v);
         inflight |= 2u;
       }
     }
