@@ -118,12 +118,23 @@ __device__ __forceinline__ void kstep32(uint32_t row_addr, uint32_t b0, uint32_t
                  : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3)
                  : "r"(row_addr + 16 * hf));
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
+    for (int r = 0; r < 3; ++r) {
       const uint32_t msk = 0x03030303u << (2 * r);
       if (kSignedB) imma_u8s8(c[4 * hf + r], a0 & msk, a1 & msk, a2 & msk, a3 & msk, b0, b1);
       else imma_u8u8(c[4 * hf + r], a0 & msk, a1 & msk, a2 & msk, a3 & msk, b0, b1);
     }
+    // field 3 needs no mask: the whole byte goes in, and fields 0..2 are subtracted once per page (finish_tiles)
+    if (kSignedB) imma_u8s8(c[4 * hf + 3], a0, a1, a2, a3, b0, b1);
+    else imma_u8u8(c[4 * hf + 3], a0, a1, a2, a3, b0, b1);
   }
+}
+
+// After the last k-step: tile 4*hf + 3 accumulated the whole bytes (all four fields); remove fields 0..2.
+__device__ __forceinline__ void finish_tiles(int (&c)[8][4]) {
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) c[4 * hf + 3][i] -= c[4 * hf][i] + c[4 * hf + 1][i] + c[4 * hf + 2][i];
 }
 
 // pk / pv: the page's row in the cache (page-table entry), read by the caller well before the copy is
@@ -284,9 +295,9 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
           mn[i] = f.y;
           smax = fmaxf(smax, f.x);
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) smax = fmaxf(smax, __shfl_xor_sync(0xffffffffu, smax, o));
-        const float fix = KFIX / smax;                     // scale >= 1e-6 by construction of the pages
+        // scales are positive, so their order is the order of their bit patterns: one integer warp reduction
+        smax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(smax)));
+        const float fix = KFIX * __frcp_rn(smax);          // scale >= 1e-6 by construction of the pages
         k_unit = smax * (1.0f / KFIX);
         *reinterpret_cast<float4 *>(&ws.sarr[4 * lane]) = make_float4(sc[0] * fix, sc[1] * fix, sc[2] * fix, sc[3] * fix);
         *reinterpret_cast<float4 *>(&ws.marr[4 * lane]) = make_float4(mn[0], mn[1], mn[2], mn[3]);
@@ -325,6 +336,7 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
         const uint32_t b1 = pack_limb(yb[0], yb[1], yb[2], yb[3], limb_sel);
         kstep32<true>(stage_u32 + I8_OFF_KREC + K_OFF_HI + lane * 32, b0, b1, cl);
       }
+      finish_tiles(cl);
       __syncwarp();      // every lane is done with the key part: request the next page's
       if (nxt < p1) {
         if (lane == 0) i8_issue_k(a, h, pk_nxt, stage_u32, bar_k);
@@ -361,9 +373,8 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
           zp[i] = f.y;
           smax = fmaxf(smax, f.x);
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) smax = fmaxf(smax, __shfl_xor_sync(0xffffffffu, smax, o));
-        const float fix = VFIX / smax;
+        smax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(smax)));
+        const float fix = VFIX * __frcp_rn(smax);
         v_unit = smax * (1.0f / VFIX);
         __syncwarp();                                      // every lane has read the key scales and mins
         *reinterpret_cast<float4 *>(&ws.sarr[4 * lane]) = make_float4(sc[0] * fix, sc[1] * fix, sc[2] * fix, sc[3] * fix);
@@ -441,6 +452,7 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
         const uint32_t b0 = ws.pb[gid * PB_RS + ks * 8 + tig], b1 = ws.pb[gid * PB_RS + ks * 8 + 4 + tig];
         kstep32<false>(stage_u32 + I8_OFF_VREC + (32 * ks + lane) * 32, b0, b1, cv);
       }
+      finish_tiles(cv);
       {
         const float u0 = v_unit;
 #pragma unroll
