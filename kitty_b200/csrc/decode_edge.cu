@@ -5,11 +5,12 @@
 namespace kitty {
 
 constexpr int EDGE_KERNEL_WARPS = 8;
+using EdgeKernelSmem = EdgeSmem<MAX_GROUP, EDGE_KERNEL_WARPS, 0>;
 
 template <int NG>
 __global__ void __launch_bounds__(EDGE_KERNEL_WARPS * 32) decode_edge_kernel(DecodeArgs a) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  EdgeSmem<EDGE_KERNEL_WARPS> &sm = *reinterpret_cast<EdgeSmem<EDGE_KERNEL_WARPS> *>(smem_raw);
+  EdgeKernelSmem &sm = *reinterpret_cast<EdgeKernelSmem *>(smem_raw);
   edge_item<NG, EDGE_KERNEL_WARPS>(a, a.P, a.C, sm, blockIdx.y, blockIdx.x, blockIdx.z);
 }
 
@@ -17,7 +18,7 @@ int launch_decode_edge(const DecodeArgs &a, cudaStream_t s) {
   static int configured = -1;     // per-process opt-in to > 48 KB dynamic shared memory, once per device
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return KITTY_E_CUDA;
-  const int smem = static_cast<int>(sizeof(EdgeSmem<EDGE_KERNEL_WARPS>));
+  const int smem = static_cast<int>(sizeof(EdgeKernelSmem));
   if (configured != dev) {
     if (cudaFuncSetAttribute(decode_edge_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
         cudaFuncSetAttribute(decode_edge_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||

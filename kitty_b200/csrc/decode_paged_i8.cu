@@ -66,14 +66,18 @@ struct I8Main {
   float qmax[4];
 };
 
+// Edge items bring their value rows in waves of 112 rows (28 KB) by bulk copies: what is left of the block's
+// shared memory once the edge's own buffers are sized for 4 query heads.
+using I8Edge = EdgeSmem<4, I8_WARPS, 112>;
+
 // A block alternates between page-pair items and edge items (sink + tail of one (batch, kv-head)); the two
 // kinds reuse the same shared memory.  The mbarriers live outside the shared region.
 struct I8Smem {
   union {
     I8Main m;
-    EdgeSmem<I8_WARPS> e;
+    I8Edge e;
   } u;
-  __align__(8) unsigned long long bar_k[I8_WARPS], bar_v[I8_WARPS];
+  __align__(8) unsigned long long bar_k[I8_WARPS], bar_v[I8_WARPS], bar_e;
   int next_item;
   // copy of the device-resident step state (plan, counters, item counts) when the launch carries one
   DecodePlan dyn_plan;
@@ -82,6 +86,7 @@ struct I8Smem {
 };
 static_assert(I8_WARPS * 4 * PART * 4 <= I8_STAGE_BYTES, "merge buffer overlays warp 0's stage");
 static_assert(sizeof(I8Smem) <= 56 * 1024, "four blocks per SM");
+static_assert(sizeof(I8Edge) <= sizeof(I8Main) + 512, "the edge buffers should not grow the block's shared memory");
 
 __device__ __forceinline__ void imma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                           uint32_t b1) {
@@ -187,12 +192,14 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
   if (lane == 0) {
     mbar_init(smem_u32(&smem.bar_k[warp]), 1);
     mbar_init(smem_u32(&smem.bar_v[warp]), 1);
+    if (warp == 0) mbar_init(smem_u32(&smem.bar_e), 1);
   }
   ws.inv[lane] = 0;
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   __syncthreads();
 
   uint32_t seq = 0;          // page pairs consumed by this warp so far (mbarrier parity)
+  uint32_t edge_phase = 0;   // completed phases of the edge row barrier (block-uniform)
   bool dead = false;         // a bounded wait ran out: stop consuming, keep the block barriers uniform
   uint32_t inflight = 0;     // bit 0: a key-part copy is in flight, bit 1: a value-part copy (warp-uniform)
   const uint32_t bar_k = smem_u32(&smem.bar_k[warp]), bar_v = smem_u32(&smem.bar_v[warp]), stage_u32 = smem_u32(&ws.stage[0]);
@@ -214,7 +221,7 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
     if (e_after > e_before) {
       // ---- edge item: one part of the sink + tail of one (batch, kv-head), by the whole block ---- //
       const int ebh = e_before / P.edge_parts, part = e_before % P.edge_parts;
-      edge_item<4, I8_WARPS>(a, P, C, smem.u.e, ebh / H, ebh % H, part);
+      edge_item<4, I8_WARPS>(a, P, C, smem.u.e, ebh / H, ebh % H, part, smem_u32(&smem.bar_e), &edge_phase);
       __syncthreads();
       ws.inv[lane] = 0;  // the slot table was overwritten: keep its entries valid positions
       continue;
