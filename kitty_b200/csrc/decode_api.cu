@@ -131,9 +131,12 @@ extern "C" int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *c
   const bool use_i8 = (impl == 0 && G <= 4);       // integer tensor-core kernel: 4 heads x (high, low) limb columns
   const int n_gt = use_i8 ? 1 : (G + 7) / 8;
   const int grid_max = (use_i8 ? 4 : 2) * sm_count();        // resident blocks per SM of the streaming kernel
-  plan_chunks(P.pe - P.pb, static_cast<int64_t>(B) * H * n_gt, grid_max, use_i8, &P.ch, &P.nchunk);
   P.fast_chunks = (impl != 1) ? 1 : 0;
   plan_edge(P.has_sink, P.has_tail, C, static_cast<int64_t>(B) * H, P.fast_chunks != 0, &P.edge_parts, &P.edge_part_tok);
+  // static item assignment (fp16 kernel): leave blocks for the edge parts so that a small call is one wave
+  const int64_t edge_blocks = use_i8 ? 0 : std::min<int64_t>(static_cast<int64_t>(B) * H * P.edge_parts, grid_max / 2);
+  plan_chunks(P.pe - P.pb, static_cast<int64_t>(B) * H * n_gt, grid_max - static_cast<int>(edge_blocks), use_i8, &P.ch,
+              &P.nchunk);
   const int has_edge = P.edge_parts > 0 ? 1 : 0;
   if (P.fast_chunks) {            // slots: [edge parts][chunks]
     P.n_slots = P.edge_parts + P.nchunk;
@@ -165,13 +168,13 @@ extern "C" int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *c
       if (int rc = launch_decode_paged_i8(a, static_cast<int>(items), static_cast<int>(n_edge), grid, s)) return rc;
     }
   } else if (P.fast_chunks) {
-    if (P.nchunk > 0) {
-      const int64_t items = static_cast<int64_t>(B) * H * n_gt * P.nchunk;
-      const int grid = static_cast<int>(std::min<int64_t>(items, grid_max));
-      if (int rc = launch_decode_paged(a, static_cast<int>(items), n_gt, grid, s)) return rc;
+    // the fp16 streaming kernel reduces the edge parts in its own grid too, after a block's page items
+    const int64_t items = static_cast<int64_t>(B) * H * n_gt * P.nchunk;
+    const int64_t n_edge = static_cast<int64_t>(B) * H * P.edge_parts;
+    if (items + n_edge > 0) {
+      const int grid = static_cast<int>(std::min<int64_t>(items + n_edge, grid_max));
+      if (int rc = launch_decode_paged(a, static_cast<int>(items), n_gt, static_cast<int>(n_edge), grid, s)) return rc;
     }
-    if (has_edge)
-      if (int rc = launch_decode_edge(a, s)) return rc;
   } else {
     const int plain_items = P.has_sink + P.nchunk + P.has_tail;
     if (plain_items > 0)

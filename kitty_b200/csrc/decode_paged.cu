@@ -23,7 +23,7 @@
 // Per (page pair, warp): 160 mma.sync and ~1450 other instructions, about 1000 of them on the
 // integer/logic pipe, which is what bounds this kernel.  It serves query groups of 5..16 heads;
 // groups of up to 4 heads use the int8 kernel (decode_paged_i8.cu).
-#include "paged_core.cuh"
+#include "decode_edge.cuh"
 
 namespace kitty {
 
@@ -62,7 +62,13 @@ __device__ __forceinline__ PairSrc pair_src(const DecodeArgs &a, int b, int h, i
   return s;
 }
 
-__global__ void __launch_bounds__(PG_WARPS * 32) decode_paged_kernel(DecodeArgs a, int n_items, int n_gt) {
+// Edge items (sink + tail parts) run in the same grid after a block's page items; their buffers overlay the
+// stages.  NGE: query heads per KV head the edge accumulators are sized for (8 or 16).
+using PagedEdge = EdgeSmem<MAX_GROUP, PG_WARPS, 0>;
+static_assert(sizeof(PagedEdge) <= PG_WARPS * PG_STAGES * STAGE_BYTES, "the edge buffers overlay the stages only");
+
+template <int NGE>
+__global__ void __launch_bounds__(PG_WARPS * 32) decode_paged_kernel(DecodeArgs a, int n_items, int n_gt, int n_edge) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   PagedSmem &sm = *reinterpret_cast<PagedSmem *>(smem_raw);
   const DecodePlan &P = a.P;
@@ -282,19 +288,30 @@ __global__ void __launch_bounds__(PG_WARPS * 32) decode_paged_kernel(DecodeArgs 
       }
     }
   }
+
+  // ---- edge items, handed out from the last block backwards (those blocks have the fewest page items) ---- //
+  PagedEdge &es = *reinterpret_cast<PagedEdge *>(smem_raw);
+  for (int e = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x); e < n_edge; e += gridDim.x) {
+    __syncthreads();     // the previous item's merge buffer / edge buffers are no longer read
+    const int ebh = e / P.edge_parts, part = e % P.edge_parts;
+    edge_item<NGE, PG_WARPS>(a, P, a.C, es, ebh / H, ebh % H, part);
+  }
 }
 
-int launch_decode_paged(const DecodeArgs &a, int n_items, int n_gt, int grid, cudaStream_t s) {
+int launch_decode_paged(const DecodeArgs &a, int n_items, int n_gt, int n_edge, int grid, cudaStream_t s) {
   static int configured = -1;     // per-process opt-in to > 48 KB dynamic shared memory, done once per device
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return KITTY_E_CUDA;
   if (configured != dev) {
-    if (cudaFuncSetAttribute(decode_paged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(decode_paged_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(sizeof(PagedSmem))) != cudaSuccess ||
+        cudaFuncSetAttribute(decode_paged_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(sizeof(PagedSmem))) != cudaSuccess)
       return KITTY_E_CUDA;
     configured = dev;
   }
-  decode_paged_kernel<<<grid, PG_WARPS * 32, sizeof(PagedSmem), s>>>(a, n_items, n_gt);
+  if (a.P.G <= 8) decode_paged_kernel<8><<<grid, PG_WARPS * 32, sizeof(PagedSmem), s>>>(a, n_items, n_gt, n_edge);
+  else decode_paged_kernel<16><<<grid, PG_WARPS * 32, sizeof(PagedSmem), s>>>(a, n_items, n_gt, n_edge);
   return cudaGetLastError() == cudaSuccess ? KITTY_OK : KITTY_E_CUDA;
 }
 

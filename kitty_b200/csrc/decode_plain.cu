@@ -4,7 +4,7 @@
 // the rotated value ring — with one thread per token (logits) and one thread
 // per channel (output).  It is slow and simple on purpose: with impl=1 it
 // computes a whole call and serves as an in-library cross-check of the streaming
-// and edge kernels.
+// and the edge reduction.
 //
 // Dequantisation is `code * scale + min` evaluated in fp32 from the fp16
 // metadata (kernels/kitty_attention.py:162-165, 317-320 of the reference do it in
@@ -185,51 +185,63 @@ __global__ void __launch_bounds__(128) decode_plain_kernel(DecodeArgs a) {
   }
 }
 
-__global__ void __launch_bounds__(128) merge_kernel(MergeArgs a) {
-  // One block per row (batch, query head); thread = channel.  The slot weights are computed
-  // once, in parallel (thread s <-> slot s), then every thread folds its channel over the slots.
+// MERGE_GROUPS slot groups per row: thread (group, channel).  Four groups when a call has few rows (then every
+// row has many slots and the launch is latency-bound), one when it has many rows of few slots.
+template <int MERGE_GROUPS>
+__global__ void __launch_bounds__(128 * MERGE_GROUPS) merge_kernel(MergeArgs a) {
+  // One block per row (batch, query head); thread = (slot group, channel).  The slot weights are computed
+  // once, in parallel (thread s <-> slot s), then every thread folds its channel over the slots of its
+  // group with eight loads in flight, and the groups are added in a fixed order.
   __shared__ float w_s[128];
   __shared__ float red[4];
+  __shared__ float part[MERGE_GROUPS][HD];
   const int64_t r = blockIdx.x;
-  const int c = threadIdx.x, lane = c & 31, warp = c >> 5;
+  const int c = threadIdx.x & (HD - 1), grp = threadIdx.x >> 7;
+  const int lane = threadIdx.x & 31, warp = (threadIdx.x >> 5) & 3;
   if (a.dyn != nullptr) a.n = a.ns = a.dyn->n_slots;
   const float *base = a.partials + ((r / a.gm) * a.ns * a.gm + r % a.gm) * PART;
   float M = -INFINITY, A = 0.f, Lsum = 0.f;
   for (int s0 = 0; s0 < a.n; s0 += 128) {           // chunks of 128 slots (one chunk in practice)
     const int nn = min(128, a.n - s0);
+    // every group computes the same weights (the loads hit L2); group 0 publishes them
     const float ms = (c < nn) ? base[(s0 + c) * a.stride_part + HD] : -INFINITY;
+    const float ls = (c < nn) ? base[(s0 + c) * a.stride_part + HD + 1] : 0.f;
     float mx = ms;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     __syncthreads();                                 // previous chunk's w_s / red are no longer read
-    if (lane == 0) red[warp] = mx;
+    if (grp == 0 && lane == 0) red[warp] = mx;
     __syncthreads();
     const float Mn = fmaxf(M, fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3])));
     const float rescale = (M == -INFINITY) ? 0.f : exp2f(M - Mn);
     M = Mn;
     const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
-    w_s[c] = w;
-    float lp = (c < nn) ? base[(s0 + c) * a.stride_part + HD + 1] * w : 0.f;
+    if (grp == 0) w_s[c] = w;
+    float lp = ls * w;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) lp += __shfl_xor_sync(0xffffffffu, lp, o);
     __syncthreads();                                 // red (max) consumed, w_s visible
-    if (lane == 0) red[warp] = lp;
+    if (grp == 0 && lane == 0) red[warp] = lp;
     __syncthreads();
     Lsum = Lsum * rescale + ((red[0] + red[1]) + (red[2] + red[3]));
     A *= rescale;
     const float *p = base + static_cast<int64_t>(s0) * a.stride_part + c;
-    int s = 0;
-    for (; s + 4 <= nn; s += 4) {
-      const float v0 = p[(s + 0) * a.stride_part], v1 = p[(s + 1) * a.stride_part];
-      const float v2 = p[(s + 2) * a.stride_part], v3 = p[(s + 3) * a.stride_part];
-      A = fmaf(v0, w_s[s], A);
-      A = fmaf(v1, w_s[s + 1], A);
-      A = fmaf(v2, w_s[s + 2], A);
-      A = fmaf(v3, w_s[s + 3], A);
+    constexpr int U = 8;
+    for (int s = grp * U; s < nn; s += U * MERGE_GROUPS) {      // slots s .. s+U-1 of this group
+      float v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) v[u] = (s + u < nn) ? p[static_cast<int64_t>(s + u) * a.stride_part] : 0.f;
+#pragma unroll
+      for (int u = 0; u < U; ++u) A = fmaf(v[u], (s + u < nn) ? w_s[s + u] : 0.f, A);
     }
-    for (; s < nn; ++s) A = fmaf(p[s * a.stride_part], w_s[s], A);
   }
-  if (a.work_counter != nullptr && r == 0 && c == 0) *a.work_counter = 0;   // ready for the next call's item hand-out
+  if (MERGE_GROUPS > 1) {
+    part[grp][c] = A;
+    __syncthreads();
+  }
+  if (a.work_counter != nullptr && r == 0 && threadIdx.x == 0) *a.work_counter = 0;   // ready for the next call's item hand-out
+  if (grp != 0) return;
+  if (MERGE_GROUPS == 4) A = (part[0][c] + part[1][c]) + (part[2][c] + part[3][c]);
   if (a.partial_out) {
     float *o = a.partial_out + r * PART;
     o[c] = A;
@@ -253,7 +265,8 @@ int launch_decode_plain(const DecodeArgs &a, int items_per_bh, cudaStream_t s) {
 
 int launch_merge(const MergeArgs &m, cudaStream_t s) {
   if (m.rows == 0) return KITTY_OK;
-  merge_kernel<<<static_cast<unsigned>(m.rows), 128, 0, s>>>(m);
+  if (m.rows <= 1024) merge_kernel<4><<<static_cast<unsigned>(m.rows), 512, 0, s>>>(m);
+  else merge_kernel<1><<<static_cast<unsigned>(m.rows), 128, 0, s>>>(m);
   return cudaGetLastError() == cudaSuccess ? KITTY_OK : KITTY_E_CUDA;
 }
 

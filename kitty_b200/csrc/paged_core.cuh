@@ -1,4 +1,4 @@
-// Building blocks shared by the streaming decode kernel and the edge kernel:
+// Building blocks shared by the streaming decode kernels and the edge reduction:
 // PTX wrappers (mbarrier, bulk async copy, mma.sync), the 2-bit-field-as-fp16-
 // subnormal operand trick and the Q K^T product of one packed key page.
 #pragma once
