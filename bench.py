@@ -53,6 +53,9 @@ def parse():
     ap.add_argument("--graph", action="store_true", help="e2e workload: replay the decode step from a CUDA graph")
     ap.add_argument("--e2e-batch", type=int, default=16, help="batch of the e2e workload")
     ap.add_argument("--e2e-steps", type=int, default=256, help="greedy steps of the e2e workload")
+    ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
+                    help="seqsplit workload: combine the partials with an NCCL all-gather + merge kernel, or inside "
+                         "the merge kernel over peer memory")
     return ap.parse_args()
 
 
@@ -343,7 +346,7 @@ def seqsplit_workload(args):
     the [28, 130] fp32 partials are all-gathered over NCCL and merged.  Launch under torchrun for N > 1."""
     global H_KV, H_Q
     import kitty_b200 as kb
-    from kitty_b200.seqsplit import seq_split_decode
+    from kitty_b200.seqsplit import PartialExchange, seq_split_decode
 
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
@@ -363,9 +366,12 @@ def seqsplit_workload(args):
     ks = torch.randn(W + K, 1, H_KV, 1, D, generator=g, device=device).to(torch.bfloat16)
     vs = torch.randn(W + K, 1, H_KV, 1, D, generator=g, device=device).to(torch.bfloat16)
 
+    xch = PartialExchange(H_Q, device) if (args.exchange == "peer" and world > 1) else None
+
     def step(i):
         cache.update(ks[i], vs[i], 0)
-        out = seq_split_decode(qs[i], lay, H_KV, D ** -0.5, rank=rank, world=world, n_common_pages=lay.PageCount_V)
+        out = seq_split_decode(qs[i], lay, H_KV, D ** -0.5, rank=rank, world=world, n_common_pages=lay.PageCount_V,
+                               exchange=xch)
         cache.quantize_decode(0)
         return out
 
@@ -389,6 +395,8 @@ def seqsplit_workload(args):
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t[0]) / K
+    if xch is not None:
+        xch.check()
     if rank == 0:
         packed = H_KV * (lay.PageCount_K * K_PAGE_BYTES + lay.PageCount_V * V_PAGE_BYTES)
         print(json.dumps({"metric": "seqsplit_layer_step_latency", "value": ms * 1e3, "unit": "us", "n_gpus": world,
@@ -396,7 +404,9 @@ def seqsplit_workload(args):
                           "packed_kv_GBps_aggregate": packed / (ms * 1e-3) / 1e9,
                           "config": {"workload": "1 layer, 28q/4kv heads, batch 1, 131072 cached tokens, sequence split "
                                                  f"over {world} GPU(s), L2 flushed between steps",
-                                     "collective": "all_gather of [28,130] fp32 per rank + merge"}}))
+                                     "collective": ("none: partials stored into every rank's buffer over NVLink by the merge "
+                                                    "kernel (kitty_lse_exchange_merge)") if xch is not None else
+                                     "all_gather of [28,130] fp32 per rank + merge"}}))
     if dist is not None:
         dist.destroy_process_group()
 

@@ -239,6 +239,24 @@ int kitty_decode_attn_static(const kitty_layer *layer, const kitty_counts *count
 int kitty_lse_merge(const float *partials, int32_t n_parts, int64_t rows, void *out, int out_dtype,
                     void *stream);
 
+/* Sequence-split combine without a collective: the log-sum-exp merge of kitty_lse_merge with the
+ * exchange of the partials done by the kernel itself over peer memory (NVLink).  No counterpart in the
+ * reference (single GPU only).
+ *
+ * Every rank owns an exchange buffer of kitty_lse_exchange_bytes(rows, world, &flag_offset) bytes that all
+ * ranks can address (CUDA IPC / VMM peer mapping, e.g. torch symmetric memory), zero-filled once before
+ * the first call.  peer_buffers is a DEVICE array of `world` pointers: entry r is rank r's buffer as
+ * mapped in this process.  All ranks call with the same rows/world and the same seq, which starts at 1
+ * and grows by one per call.  The kernel stores this rank's partial (fp32 [rows, 130], the partial_out
+ * layout) into every rank's buffer, raises a per-row flag, waits at most one second for the other ranks'
+ * flags and writes out [rows, 128].  A wait that runs out sets *status (device int32, may be null) and
+ * leaves the row unwritten.  rows <= KITTY_EXCHANGE_MAX_ROWS so that every block of the launch is
+ * resident (a block waits only for the same row on other GPUs). */
+#define KITTY_EXCHANGE_MAX_ROWS 1024
+int64_t kitty_lse_exchange_bytes(int64_t rows, int32_t world, int64_t *flag_offset);
+int kitty_lse_exchange_merge(const float *local_partial, int64_t rows, void *const *peer_buffers, int32_t rank,
+                             int32_t world, int32_t seq, void *out, int out_dtype, int32_t *status, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -6,8 +6,11 @@ sink tokens, the last rank the tail (extra key pages, Q-buffers, value ring) —
 the last rank is the one that receives appended tokens and performs flushes.
 Every rank emits (acc[128], max, sum) per query head, the [B, H_Q, 130] fp32
 partials are all-gathered (NCCL over NVLink on GPUs) and merged identically on
-every rank.  The exchange is 520 bytes per query head per rank: latency-bound,
-one collective per layer, no peer-memory kernels.
+every rank.  The exchange is 520 bytes per query head per rank: latency-bound.
+Two ways to do it: one NCCL all-gather plus the merge kernel (default), or a
+`PartialExchange`, where the merge kernel itself stores the partials into every
+rank's buffer over NVLink and waits for the others (kitty_lse_exchange_merge) —
+no collective launch at all.
 """
 from __future__ import annotations
 
@@ -47,8 +50,55 @@ def _cuda_merge(parts, dtype):
     return lse_merge(parts, dtype)
 
 
+class PartialExchange:
+    """Peer-addressable buffers for kitty_lse_exchange_merge: one symmetric-memory allocation per rank, every
+    rank's copy mapped into every process (torch.distributed._symmetric_memory), zeroed once.  `rows` = B * H_Q."""
+
+    def __init__(self, rows: int, device, group=None):
+        import ctypes
+
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        from . import _lib
+
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world, self.rows = dist.get_rank(group), dist.get_world_size(group), rows
+        off = ctypes.c_int64(0)
+        nbytes = _lib.lib().kitty_lse_exchange_bytes(rows, self.world, ctypes.byref(off))
+        if nbytes < 0:
+            _lib.check(int(nbytes), "kitty_lse_exchange_bytes")
+        self.buf = symm.empty((int(nbytes) + 3) // 4, dtype=torch.float32, device=device)
+        self.buf.zero_()
+        self.handle = symm.rendezvous(self.buf, group.group_name)
+        self.peer_table = int(self.handle.buffer_ptrs_dev)        # device array of `world` buffer addresses
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.seq = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group)                                       # every buffer is zero before anyone writes
+
+    def merge(self, part: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        """part: this rank's fp32 [B, H_Q, 130] partial.  Returns [B, 1, H_Q, 128] (identical on every rank)."""
+        from . import _lib
+
+        assert part.dtype == torch.float32 and part.is_contiguous() and part.shape[0] * part.shape[1] == self.rows
+        B, H_Q, W = part.shape
+        out = torch.empty((B, 1, H_Q, W - 2), dtype=out_dtype, device=part.device)
+        self.seq += 1
+        rc = _lib.lib().kitty_lse_exchange_merge(part.data_ptr(), self.rows, self.peer_table, self.rank, self.world,
+                                                 self.seq, out.data_ptr(), _lib.dtype_code(out_dtype),
+                                                 self.status.data_ptr(), _lib.stream_ptr(part.device))
+        _lib.check(rc, "kitty_lse_exchange_merge")
+        return out
+
+    def check(self) -> None:
+        """Synchronise and raise if a bounded wait of an earlier merge ran out."""
+        if int(self.status.item()) != 0:
+            raise RuntimeError("kitty_lse_exchange_merge: a peer's partial did not arrive within the wait limit")
+
+
 def seq_split_decode(query: torch.Tensor, layer, num_kv_heads: int, scaling: float, *, rank: int, world: int,
-                     n_common_pages: int, group=None,
+                     n_common_pages: int, group=None, exchange: Optional[PartialExchange] = None,
                      partial_fn: Optional[Callable] = None, merge_fn: Optional[Callable] = None) -> torch.Tensor:
     """Decode attention of `query` [B, H_Q, 1, D] over a sequence whose common packed pages
     [0, n_common_pages) are split over `world` ranks.  `layer` is this rank's KVCache_Layer (only its own
@@ -60,6 +110,8 @@ def seq_split_decode(query: torch.Tensor, layer, num_kv_heads: int, scaling: flo
     lo, hi = split_pages(n_common_pages, world)[rank]
     part = (partial_fn or _cuda_partial)(query, layer, num_kv_heads, scaling, lo, hi, rank_flags(rank, world))
     part = part.contiguous()
+    if exchange is not None:
+        return exchange.merge(part, query.dtype)
     flat = torch.empty((world * part.shape[0],) + tuple(part.shape[1:]), dtype=part.dtype, device=part.device)
     if world > 1:
         dist.all_gather_into_tensor(flat, part, group=group)      # rank r's rows land at [r*B, (r+1)*B)

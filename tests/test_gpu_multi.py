@@ -1,5 +1,6 @@
-"""Sequence-split decode on 2 GPUs (NCCL all-gather + kitty_lse_merge) against the
-single-GPU call.  Skipped when fewer than 2 GPUs are visible."""
+"""Sequence-split decode on 2 GPUs against the single-GPU call, both ways of combining the partials: NCCL
+all-gather + kitty_lse_merge, and the peer-memory exchange inside the merge kernel (kitty_lse_exchange_merge).
+Skipped when fewer than 2 GPUs are visible."""
 import os
 import socket
 import types
@@ -22,7 +23,7 @@ def _worker(rank, world, port, q_out):
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     import kitty_b200 as kb
-    from kitty_b200.seqsplit import seq_split_decode
+    from kitty_b200.seqsplit import PartialExchange, seq_split_decode
 
     h_kv, h_q, B, L = 4, 28, 1, 32 + 40 * 128 + 50          # the long-context shape: 28 query / 4 KV heads
     cfg = types.SimpleNamespace(num_hidden_layers=1, head_dim=128, num_key_value_heads=h_kv, num_attention_heads=h_q,
@@ -40,7 +41,16 @@ def _worker(rank, world, port, q_out):
     out = seq_split_decode(q, lay, h_kv, 128 ** -0.5, rank=rank, world=world, n_common_pages=lay.PageCount_V)
     torch.cuda.synchronize(dev)
     err = (out.float() - full.float()).abs().max().item() / full.float().abs().max().item()
-    q_out.put((rank, err))
+    # the same step with the partials exchanged by the merge kernel itself, several calls in a row
+    xch = PartialExchange(B * h_q, dev)
+    err_x = 0.0
+    for _ in range(5):
+        out_x = seq_split_decode(q, lay, h_kv, 128 ** -0.5, rank=rank, world=world, n_common_pages=lay.PageCount_V,
+                                 exchange=xch)
+        torch.cuda.synchronize(dev)
+        err_x = max(err_x, (out_x.float() - out.float()).abs().max().item() / out.float().abs().max().item())
+    xch.check()
+    q_out.put((rank, err, err_x))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -62,4 +72,5 @@ def test_two_gpu_sequence_split():
     for p in procs:
         p.join(120)
         assert p.exitcode == 0
-    assert all(e <= 1e-2 for _, e in res), res
+    assert all(e <= 1e-2 for _, e, _ in res), res
+    assert all(ex <= 4e-3 for _, _, ex in res), res       # same partials; the sums may differ in the last bf16 bit

@@ -353,3 +353,32 @@ def test_full_size_32k_properties(kb):
     got = lay.KeyCache.cpu().numpy().reshape(-1, h_kv, 5248)
     for p in range(3):
         assert np.array_equal(got[b * lay.MAX_PAGE + p, h], rec[p])
+
+
+def test_exchange_merge_single_rank_equals_lse_merge(kb):
+    """World of one: the peer-memory combine publishes to its own buffer, waits for its own flag and
+    normalises — the same result as kitty_lse_merge of one part, over several calls (both buffer halves)."""
+    import ctypes
+
+    from kitty_b200 import _lib
+
+    rows = 28
+    off = ctypes.c_int64(0)
+    nbytes = _lib.lib().kitty_lse_exchange_bytes(rows, 1, ctypes.byref(off))
+    assert nbytes == 2 * rows * 130 * 4 + 2 * rows * 4 and off.value == 2 * rows * 130 * 4
+    buf = torch.zeros(nbytes // 4, dtype=torch.float32, device=DEV)
+    table = torch.tensor([buf.data_ptr()], dtype=torch.int64, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    g = torch.Generator().manual_seed(4)
+    for seq in range(1, 5):
+        part = torch.randn(1, rows, 130, generator=g).to(DEV)
+        part[..., 129] = part[..., 129].abs() + 0.5
+        out = torch.empty(1, 1, rows, 128, dtype=torch.float32, device=DEV)
+        rc = _lib.lib().kitty_lse_exchange_merge(part.data_ptr(), rows, table.data_ptr(), 0, 1, seq, out.data_ptr(),
+                                                 _lib.KITTY_F32, status.data_ptr(), _lib.stream_ptr(torch.device(DEV)))
+        assert rc == 0
+        want = kb.lse_merge(part.view(1, 1, rows, 130).contiguous(), torch.float32)
+        assert torch.allclose(out, want, rtol=1e-6, atol=0)
+    assert int(status.item()) == 0
+    assert _lib.lib().kitty_lse_exchange_merge(part.data_ptr(), 2000, table.data_ptr(), 0, 1, 9, out.data_ptr(),
+                                               _lib.KITTY_F32, None, None) == _lib.KITTY_E_BADARG
