@@ -25,7 +25,7 @@ class KittyCache(Cache):
     is_compileable = False
 
     def __init__(self, config, max_batch_size: int, max_length: int, device="cuda", selection: str = "fused",
-                 div_mode: int = _lib.DIV_IEEE) -> None:
+                 div_mode: int = _lib.DIV_IEEE, num_pages: Optional[int] = None, page_order=None) -> None:
         try:
             super().__init__(layers=[])
         except TypeError:           # older transformers: Cache.__init__() takes no arguments
@@ -47,7 +47,8 @@ class KittyCache(Cache):
         self.kv_cache: list[KVCache_Layer] = [
             KVCache_Layer(MAX_BS=max_batch_size, MAX_LEN=max_length, H_KV=self.num_key_value_heads, D=self.head_dim,
                           D_BOOSTED=self.d_boosted, LOW_BIT=self.low_bit, HIGH_BIT=self.high_bit,
-                          PAGE_SIZE=self.page_size, S=self.sink_length, device=device)
+                          PAGE_SIZE=self.page_size, S=self.sink_length, device=device, num_pages=num_pages,
+                          page_order=page_order)
             for _ in range(self.num_hidden_layers)]
 
     # ------------------------------------------------------------------ #
@@ -109,6 +110,7 @@ class KittyCache(Cache):
         local_v = min(P, L - sink)
         qbuf_v = (L - sink - local_v) % P
         pages_v = (L - sink - local_v - qbuf_v) // P
+        lay.ensure_pages(pages_k + 1, pages_v + 1)          # the prompt's pages and the one the next flush fills
         rc = _lib.lib().kitty_prefill_tails(lay.c_layer(), k.data_ptr(), v.data_ptr(), _lib.dtype_code(k.dtype),
                                             k.stride(0), k.stride(1), k.stride(2), v.stride(0), v.stride(1),
                                             v.stride(2), B, L, sink, qbuf_k, local_v, qbuf_v,
@@ -153,6 +155,13 @@ class KittyCache(Cache):
         if fv:
             lay.PageCount_V += 1
             lay.Q_Buffer_Count_V = 0
+        lay.ensure_pages(lay.PageCount_K + 1, lay.PageCount_V + 1)      # keep the next flush's page assigned
+
+    def reset(self) -> None:
+        """Forget every sequence (pooled mode: the page rows go back to the pools).  The reference builds a new
+        cache per generate() call instead (latency_benchmarking/benchmark_kitty.py:154-160)."""
+        for lay in self.kv_cache:
+            lay.release_pages()
 
     # -- decode step with device-resident state (for CUDA-graph capture) ----------------- #
     # The three calls of a decode step (update, kitty_attention_forward, quantize_decode) pass the
@@ -214,6 +223,7 @@ class KittyCache(Cache):
             lay.PageCount_K, lay.PageCount_V, lay.Sink_Count = n.PageCount_K, n.PageCount_V, n.Sink_Count
             lay.Q_Buffer_Count_K, lay.Q_Buffer_Count_V = n.Q_Buffer_Count_K, n.Q_Buffer_Count_V
             lay.Local_Count_V, lay.Write_Offset_Local_V = n.Local_Count_V, n.Write_Offset_Local_V
+            lay.ensure_pages(lay.PageCount_K + 1, lay.PageCount_V + 1)
         self._step_host = None
 
     @staticmethod

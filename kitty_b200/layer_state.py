@@ -20,9 +20,38 @@ PAGE_SIZE = 128
 SINK = 32
 
 
+class PagePool:
+    """Free list of page rows of one cache tensor (host side).  The reference allocates MAX_BS * ceil(MAX_LEN / 128)
+    rows per layer and an identity page table (utils_kv_per_layer.py:48-59); behind the same table a pool can hold
+    fewer rows than that worst case and hand them out as sequences grow.  `order` fixes the hand-out order
+    (tests pass a permutation so that the mapping is not the identity)."""
+
+    def __init__(self, num_pages: int, order: Optional[list] = None):
+        ids = list(range(num_pages)) if order is None else list(order)
+        if sorted(ids) != list(range(num_pages)):
+            raise ValueError("order must be a permutation of range(num_pages)")
+        self.num_pages = num_pages
+        self._free = ids[::-1]            # pop() hands out ids in `order`
+
+    def available(self) -> int:
+        return len(self._free)
+
+    def alloc(self, n: int) -> list:
+        if n > len(self._free):
+            raise MemoryError(f"page pool exhausted: {n} pages wanted, {len(self._free)} of {self.num_pages} free")
+        return [self._free.pop() for _ in range(n)]
+
+    def free(self, ids) -> None:
+        ids = [int(i) for i in ids]
+        if any(i < 0 or i >= self.num_pages for i in ids) or set(ids) & set(self._free) or len(set(ids)) != len(ids):
+            raise ValueError("freeing a page that is not allocated")
+        self._free.extend(reversed(ids))
+
+
 class KVCache_Layer:
     def __init__(self, MAX_BS: int, MAX_LEN: int, H_KV: int, D: int, D_BOOSTED: int, LOW_BIT: int, HIGH_BIT: int,
-                 PAGE_SIZE: int, S: int, device="cuda"):
+                 PAGE_SIZE: int, S: int, device="cuda", num_pages: Optional[int] = None,
+                 page_order: Optional[list] = None):
         if (PAGE_SIZE, D, D_BOOSTED, S, LOW_BIT, HIGH_BIT) != (128, 128, 32, 32, 2, 4):
             raise ValueError("kitty_b200 kernels are built for PAGE_SIZE=128, D=128, D_BOOSTED=32, S=32, 2/4 bit; got "
                              f"{(PAGE_SIZE, D, D_BOOSTED, S, LOW_BIT, HIGH_BIT)}")
@@ -38,14 +67,26 @@ class KVCache_Layer:
         row = PAGE_SIZE * LOW_BIT // 8                       # bytes of one channel row (keys) / token row (values)
         self.bytes_per_page_K = H_KV * (row * (D + D_BOOSTED) + D)
         self.bytes_per_page_V = H_KV * row * PAGE_SIZE
-        n = MAX_BS * self.MAX_PAGE
+        # Static mode (num_pages None, the reference's): one row per (sequence, page) and identity tables.
+        # Pooled mode: num_pages rows per cache tensor, table entries assigned by ensure_pages() as the
+        # sequences grow; the kernels only ever see the tables.
+        self.pooled = num_pages is not None
+        n = num_pages if self.pooled else MAX_BS * self.MAX_PAGE
+        self.pool_K = PagePool(n, page_order) if self.pooled else None
+        self.pool_V = PagePool(n, page_order) if self.pooled else None
+        self._assigned_K = 0              # pages [0, _assigned_*) of every sequence have a row
+        self._assigned_V = 0
         z = dict(device=dev)
         self.KeyCache = torch.zeros((n, self.bytes_per_page_K), dtype=torch.uint8, **z)
         self.KeyCache_metadata = torch.zeros((n, H_KV, D, 2), dtype=torch.float16, **z)
         self.ValueCache = torch.zeros((n, self.bytes_per_page_V), dtype=torch.uint8, **z)
         self.ValueCache_metadata = torch.zeros((n, H_KV, PAGE_SIZE, 2), dtype=torch.float16, **z)
-        self.PageTable_K = torch.arange(n, dtype=torch.int64, **z).view(MAX_BS, self.MAX_PAGE).contiguous()
-        self.PageTable_V = self.PageTable_K.clone()
+        if self.pooled:
+            self.PageTable_K = torch.zeros((MAX_BS, self.MAX_PAGE), dtype=torch.int64, **z)
+            self.PageTable_V = torch.zeros((MAX_BS, self.MAX_PAGE), dtype=torch.int64, **z)
+        else:
+            self.PageTable_K = torch.arange(n, dtype=torch.int64, **z).view(MAX_BS, self.MAX_PAGE).contiguous()
+            self.PageTable_V = self.PageTable_K.clone()
         self.PageCount_K = 0
         self.PageCount_V = 0
         self.Sink_Buffer_K = torch.zeros((MAX_BS, H_KV, S, D), dtype=torch.float16, **z)
@@ -69,6 +110,37 @@ class KVCache_Layer:
         seqlen_v = self.PageCount_V * self.PAGE_SIZE + self.Sink_Count + self.Q_Buffer_Count_V + self.Local_Count_V
         assert seqlen_k == seqlen_v, f"seqlen_K: {seqlen_k}, seqlen_V: {seqlen_v}"
         return seqlen_k
+
+    # -- pooled page rows ----------------------------------------------------- #
+    def ensure_pages(self, pages_k: int, pages_v: int) -> None:
+        """Pooled mode: make sure pages [0, pages_k) / [0, pages_v) of every sequence have a cache row (capped at
+        MAX_PAGE).  New table entries are written with one small host-to-device copy per tensor, in stream order
+        before the kernels that use them.  A no-op in static mode."""
+        if not self.pooled:
+            return
+        for which, want in (("K", min(pages_k, self.MAX_PAGE)), ("V", min(pages_v, self.MAX_PAGE))):
+            have = getattr(self, "_assigned_" + which)
+            if want <= have:
+                continue
+            pool = getattr(self, "pool_" + which)
+            ids = pool.alloc((want - have) * self.MAX_BS)
+            block = torch.tensor(ids, dtype=torch.int64).view(want - have, self.MAX_BS).t().contiguous()
+            getattr(self, "PageTable_" + which)[:, have:want].copy_(block.to(self.device, non_blocking=False))
+            setattr(self, "_assigned_" + which, want)
+
+    def release_pages(self) -> None:
+        """Pooled mode: give every assigned row back and clear the counters (the sequences are finished)."""
+        if self.pooled:
+            for which in ("K", "V"):
+                have = getattr(self, "_assigned_" + which)
+                if have:
+                    ids = getattr(self, "PageTable_" + which)[:, :have].t().reshape(-1).tolist()
+                    getattr(self, "pool_" + which).free(ids)
+                setattr(self, "_assigned_" + which, 0)
+        self.PageCount_K = self.PageCount_V = 0
+        self.Sink_Count = self.Q_Buffer_Count_K = self.Q_Buffer_Count_V = 0
+        self.Local_Count_V = self.Write_Offset_Local_V = 0
+        self.key_states = self.value_states = None
 
     # -- C-ABI views --------------------------------------------------------- #
     def c_layer(self) -> "_lib.KittyLayer":

@@ -154,3 +154,47 @@ def test_graphed_decoder_follows_the_eager_adapter(kb):
     assert dec.graph is not None
     assert cache.get_seq_length(0) == ids.shape[1] + 23
     assert torch.equal(got, want)
+
+
+def test_pooled_pages_match_identity_tables(kb):
+    """A cache whose page rows come from a shuffled pool (fewer rows than the static worst case) must give the same
+    attention outputs and hold the same page bytes, seen through its tables, as the reference-style static cache —
+    across prefill, decode steps with key and value flushes, and a reset followed by a second batch."""
+    B, h_kv, h_q, layers, max_len = 2, 2, 8, 1, 4096            # static: 2 * 32 rows per tensor
+    cfg = _cfg(layers, h_kv, h_q)
+    mod = types.SimpleNamespace(num_attention_heads=h_q, num_key_value_heads=h_kv)
+    g = torch.Generator().manual_seed(3)
+    order = torch.randperm(12, generator=g).tolist()
+    pooled = kb.get_kvcache_kitty(cfg, B, max_len, device=DEV, num_pages=12, page_order=order)
+    for round_ in range(2):
+        L = 32 + 128 * 2 + 120 + 7 * round_
+        static = kb.get_kvcache_kitty(cfg, B, max_len, device=DEV)
+        k, v = make_kv(B, h_kv, L, 128, 40 + round_)
+        for c in (static, pooled):
+            assert c.update(k.to(DEV), v.to(DEV), 0) is True
+            c.quantize_prefill(0)
+        for s in range(140):
+            kk, vv, q = _inputs(B, h_kv, h_q, s + 1000 * round_, 0)
+            outs = []
+            for c in (static, pooled):
+                c.update(kk, vv, 0)
+                outs.append(kb.kitty_attention_forward(mod, q, c.kv_cache[0], 0.09)[0])
+                c.quantize_decode(0)
+            assert torch.equal(outs[0], outs[1]), (round_, s)
+        ls, lp = static.kv_cache[0], pooled.kv_cache[0]
+        assert [getattr(ls, n) for n in COUNTERS] == [getattr(lp, n) for n in COUNTERS]
+        assert ls.PageCount_K >= 4 and ls.PageCount_V >= 3
+        for cache_name, table_name, count in (("KeyCache", "PageTable_K", ls.PageCount_K),
+                                              ("ValueCache", "PageTable_V", ls.PageCount_V)):
+            rows_s = getattr(ls, cache_name)[getattr(ls, table_name)[:, :count].reshape(-1)]
+            rows_p = getattr(lp, cache_name)[getattr(lp, table_name)[:, :count].reshape(-1)]
+            assert torch.equal(rows_s, rows_p), cache_name
+        assert not torch.equal(lp.PageTable_K[:, :ls.PageCount_K], ls.PageTable_K[:, :ls.PageCount_K])
+        assert lp.pool_K.available() == 12 - B * (ls.PageCount_K + 1)
+        pooled.reset()
+        assert lp.pool_K.available() == 12 and lp.pool_V.available() == 12 and pooled.get_seq_length(0) == 0
+    small = kb.get_kvcache_kitty(cfg, B, max_len, device=DEV, num_pages=4)
+    k, v = make_kv(B, h_kv, 32 + 128 * 3, 128, 50)
+    small.update(k.to(DEV), v.to(DEV), 0)
+    with pytest.raises(MemoryError):
+        small.quantize_prefill(0)

@@ -13,7 +13,9 @@ from tests.helpers import COUNTERS
 class FakeLayer:
     """Counters and geometry only; no device buffers."""
 
-    def __init__(self, MAX_BS, MAX_LEN, H_KV, D, D_BOOSTED, LOW_BIT, HIGH_BIT, PAGE_SIZE, S, device="cuda"):
+    def __init__(self, MAX_BS, MAX_LEN, H_KV, D, D_BOOSTED, LOW_BIT, HIGH_BIT, PAGE_SIZE, S, device="cuda",
+                 num_pages=None, page_order=None):
+        self.ensured = []
         self.MAX_BS, self.MAX_LEN, self.H_KV, self.D, self.D_BOOSTED = MAX_BS, MAX_LEN, H_KV, D, D_BOOSTED
         self.PAGE_SIZE, self.S, self.device = PAGE_SIZE, S, torch.device("cpu")
         self.MAX_PAGE = -(-MAX_LEN // PAGE_SIZE)
@@ -26,6 +28,9 @@ class FakeLayer:
 
     def c_layer(self):
         return None
+
+    def ensure_pages(self, pages_k, pages_v):
+        self.ensured.append((pages_k, pages_v))
 
     def c_counts(self):
         return tuple(getattr(self, c) for c in COUNTERS)
@@ -110,3 +115,20 @@ def test_update_rejects_multi_token_decode(fake):
         cache.quantize_prefill(0)
     assert cache.get_mask_sizes(torch.arange(1), 0) == (41, 0)
     assert len(cache) == 1 and cache.get_max_cache_shape() == 512
+
+
+def test_page_pool_hands_out_and_takes_back():
+    from kitty_b200.layer_state import PagePool
+
+    pool = PagePool(6, order=[4, 0, 5, 1, 3, 2])
+    assert pool.alloc(3) == [4, 0, 5] and pool.available() == 3
+    pool.free([0, 4])
+    assert pool.available() == 5
+    assert sorted(pool.alloc(5)) == [0, 1, 2, 3, 4]
+    with pytest.raises(MemoryError):
+        pool.alloc(1)
+    with pytest.raises(ValueError):
+        PagePool(3, order=[0, 0, 1])
+    pool.free([5])
+    with pytest.raises(ValueError):
+        pool.free([5])                 # already free
