@@ -382,3 +382,43 @@ def test_exchange_merge_single_rank_equals_lse_merge(kb):
     assert int(status.item()) == 0
     assert _lib.lib().kitty_lse_exchange_merge(part.data_ptr(), 2000, table.data_ptr(), 0, 1, 9, out.data_ptr(),
                                                _lib.KITTY_F32, None, None) == _lib.KITTY_E_BADARG
+
+
+def test_full_size_131k_group_of_7_properties(kb):
+    """The long-context shape (28 query / 4 KV heads, batch 1, 131072 cached tokens: 1023 key pages, 1022 value
+    pages): the fp16 streaming kernel agrees with the plain kernel, an 8-way split over the pages merges to the same
+    result, and one head agrees with the oracle."""
+    h_kv, h_q, B, L = 4, 28, 1, 131072
+    g = torch.Generator().manual_seed(77)
+    k = torch.randn(B, h_kv, L, 128, generator=g)
+    for h in range(h_kv):
+        k[:, h, :, torch.randperm(128, generator=g)[:4]] *= 8.0
+    v = torch.randn(B, h_kv, L, 128, generator=g)
+    k, v = k.bfloat16(), v.bfloat16()
+    cache = kb.KittyCache(_cfg(1, h_kv, h_q), B, L + 256, device=DEV)
+    cache.update(k.to(DEV), v.to(DEV), 0)
+    cache.quantize_prefill(0)
+    lay = cache.kv_cache[0]
+    assert (lay.PageCount_K, lay.PageCount_V, lay.Q_Buffer_Count_K, lay.Q_Buffer_Count_V) == (1023, 1022, 96, 96)
+    kt, vt = torch.randn(B, h_kv, 1, 128, generator=g).bfloat16(), torch.randn(B, h_kv, 1, 128, generator=g).bfloat16()
+    cache.update(kt.to(DEV), vt.to(DEV), 0)
+    q = torch.randn(B, h_q, 1, 128, generator=g).bfloat16().to(DEV)
+    sc = 128 ** -0.5
+    fast = kb.decode_attention(q, lay, h_kv, sc).float().cpu().numpy()
+    plain = kb.decode_attention(q, lay, h_kv, sc, impl=1).float().cpu().numpy()
+    assert ko.rel_err(fast, plain) <= ATTN_TOL
+    from kitty_b200.seqsplit import rank_flags, split_pages
+
+    parts = torch.empty(8, B, h_q, 130, dtype=torch.float32, device=DEV)
+    for r, (lo, hi) in enumerate(split_pages(lay.PageCount_V, 8)):
+        kb.decode_attention(q, lay, h_kv, sc, page_begin=lo, page_end=hi, flags=rank_flags(r, 8), partial_out=parts[r])
+    merged = kb.lse_merge(parts, torch.bfloat16).float().cpu().numpy()
+    assert ko.rel_err(merged, fast) <= ATTN_TOL
+    view = types.SimpleNamespace(D=128, D_BOOSTED=32, H_KV=h_kv, **{n: getattr(lay, n).cpu().numpy() for n in BUFFERS},
+                                 **{c: getattr(lay, c) for c in COUNTERS})
+    h = 2
+    K, V = ko.gather_kv(view, 0, h)
+    qh = q[0, h * 7:(h + 1) * 7, 0].float().cpu().numpy()
+    m, l, acc = ko.attention_partial(qh, K, V, sc)
+    assert ko.rel_err(fast[0, 0, h * 7:(h + 1) * 7], acc / l[:, None]) <= ATTN_TOL
+    assert kb.workspace_status(lay) == 0
