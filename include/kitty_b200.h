@@ -253,6 +253,15 @@ int kitty_lse_merge(const float *partials, int32_t n_parts, int64_t rows, void *
  * leaves the row unwritten.  rows <= KITTY_EXCHANGE_MAX_ROWS so that every block of the launch is
  * resident (a block waits only for the same row on other GPUs). */
 #define KITTY_EXCHANGE_MAX_ROWS 1024
+/* kitty_decode_attn of this rank's part of the sequence (page_begin/page_end/flags as there) whose final merge
+ * kernel also does the exchange above: one call and one launch fewer per layer than kitty_decode_attn with
+ * partial_out followed by kitty_lse_exchange_merge.  B*h_q <= KITTY_EXCHANGE_MAX_ROWS.  A rank whose part is
+ * empty still has to call (it contributes an empty partial). */
+int kitty_decode_attn_exchange(const kitty_layer *layer, const kitty_counts *counts, const void *query, int q_dtype,
+                               int32_t B, int32_t h_q, float scaling, void *out, int out_dtype, void *workspace,
+                               int64_t workspace_bytes, int32_t page_begin, int32_t page_end, int32_t flags, int impl,
+                               void *const *peer_buffers, int32_t rank, int32_t world, int32_t seq, int32_t *status,
+                               void *stream);
 int64_t kitty_lse_exchange_bytes(int64_t rows, int32_t world, int64_t *flag_offset);
 int kitty_lse_exchange_merge(const float *local_partial, int64_t rows, void *const *peer_buffers, int32_t rank,
                              int32_t world, int32_t seq, void *out, int out_dtype, int32_t *status, void *stream);

@@ -19,9 +19,11 @@ MAX_KV_GROUP = 16
 
 def decode_attention(query: torch.Tensor, kv_cache: KVCache_Layer, num_kv_heads: int, scaling: float, *,
                      out: Optional[torch.Tensor] = None, page_begin: int = 0, page_end: int = -1, flags: int = 3,
-                     partial_out: Optional[torch.Tensor] = None, impl: int = 0) -> Optional[torch.Tensor]:
+                     partial_out: Optional[torch.Tensor] = None, impl: int = 0, exchange=None) -> Optional[torch.Tensor]:
     """Launch the decode-attention kernels.  With `partial_out` (fp32 [B, H_Q, 130]) the un-normalised partial
-    result of the selected part of the sequence is written there and nothing is returned."""
+    result of the selected part of the sequence is written there and nothing is returned.  With `exchange` (a
+    seqsplit.PartialExchange) the call reduces this rank's part and its merge kernel combines it with the other
+    ranks' parts over peer memory: the returned tensor is the complete result."""
     assert query.is_contiguous(), "Query tensor must be contiguous."
     B, H_Q, t_query, D = query.size()
     assert t_query == 1, "Only decoding step with t_query=1 is supported."
@@ -41,6 +43,16 @@ def decode_attention(query: torch.Tensor, kv_cache: KVCache_Layer, num_kv_heads:
         assert partial_out.dtype == torch.float32 and partial_out.is_contiguous()
         assert tuple(partial_out.shape) == (B, H_Q, D + 2)
     layer, counts = kv_cache.c_layer(), kv_cache.c_counts()
+    if exchange is not None:
+        assert partial_out is None and B * H_Q == exchange.rows
+        exchange.seq += 1
+        rc = _lib.lib().kitty_decode_attn_exchange(layer, counts, query.data_ptr(), _lib.dtype_code(query.dtype), B, H_Q,
+                                                   float(scaling), out_ptr, out_code, ws.data_ptr(), ws.numel(),
+                                                   page_begin, page_end, flags, impl, exchange.peer_table,
+                                                   exchange.rank, exchange.world, exchange.seq,
+                                                   exchange.status.data_ptr(), _lib.stream_ptr(query.device))
+        _lib.check(rc, "kitty_decode_attn_exchange")
+        return out
     rc = _lib.lib().kitty_decode_attn(layer, counts, query.data_ptr(), _lib.dtype_code(query.dtype), B, H_Q,
                                       float(scaling), out_ptr, out_code, ws.data_ptr(), ws.numel(), page_begin,
                                       page_end, flags, None if partial_out is None else partial_out.data_ptr(), impl,

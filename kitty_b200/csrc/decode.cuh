@@ -48,6 +48,14 @@ struct DecodeArgs {
 
 // Merge n partials per row.  Row r's partial s lives at
 //   base + ((r / gm) * ns * gm + r % gm) * PART + s * stride_part   (floats).
+// Peer-memory exchange of the merged partials (sequence split over GPUs); peers == nullptr: none.
+struct XchgDesc {
+  float *const *peers;       // device array [world]: base address of every rank's exchange buffer
+  int64_t flag_offset;       // byte offset of the flag area inside an exchange buffer
+  int32_t rank, world, seq;
+  int32_t *status;           // or null: set non-zero when a wait ran out
+};
+
 struct MergeArgs {
   const float *partials;
   int64_t rows, stride_part;
@@ -57,6 +65,7 @@ struct MergeArgs {
   float *partial_out; // [rows, PART] or null: merged but un-normalised
   int32_t *work_counter;  // or null: word the streaming kernel used to hand out items; reset to 0 here
   const kitty_step_state *dyn;   // or null.  Non-null: the number of slots is read from it on the device
+  XchgDesc x;                    // x.peers non-null: exchange the row's partial with the other ranks before writing out
 };
 
 int launch_decode_plain(const DecodeArgs &a, int items_per_bh, cudaStream_t s);

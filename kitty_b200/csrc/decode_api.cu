@@ -90,10 +90,10 @@ extern "C" int64_t kitty_decode_workspace_bytes(int32_t B, int32_t h_kv, int32_t
   return WS_HEADER + bh * (cap + EDGE_PARTS_MAX) * G * PART * static_cast<int64_t>(sizeof(float));
 }
 
-extern "C" int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *counts, const void *query, int q_dtype,
-                                 int32_t B, int32_t h_q, float scaling, void *out, int out_dtype, void *workspace,
-                                 int64_t workspace_bytes, int32_t page_begin, int32_t page_end, int32_t flags,
-                                 float *partial_out, int impl, void *stream) {
+static int decode_attn_core(const kitty_layer *layer, const kitty_counts *counts, const void *query, int q_dtype,
+                            int32_t B, int32_t h_q, float scaling, void *out, int out_dtype, void *workspace,
+                            int64_t workspace_bytes, int32_t page_begin, int32_t page_end, int32_t flags,
+                            float *partial_out, int impl, const XchgDesc *xchg, void *stream) {
   if (!layer || !counts || !query || !workspace) return KITTY_E_BADARG;
   if (!out && !partial_out) return KITTY_E_BADARG;
   if (layer->head_dim != HD || layer->page_size != PAGE || layer->d_boost != DB || layer->sink_size != SINK)
@@ -147,7 +147,7 @@ extern "C" int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *c
     P.chunk_slot0 = P.has_sink;
     P.edge_slot = 0;
   }
-  if (P.n_slots == 0 && !partial_out) return KITTY_E_BADARG;                      // nothing to attend to
+  if (P.n_slots == 0 && !partial_out && !xchg) return KITTY_E_BADARG;             // nothing to attend to
 
   const int64_t need = WS_HEADER + static_cast<int64_t>(B) * H * P.n_slots * G * PART * static_cast<int64_t>(sizeof(float));
   if (workspace_bytes < need) return KITTY_E_WORKSPACE;
@@ -193,7 +193,35 @@ extern "C" int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *c
   m.partial_out = partial_out;
   m.work_counter = a.status + 1;
   m.dyn = nullptr;
+  m.x = xchg ? *xchg : XchgDesc{};
   return launch_merge(m, s);
+}
+
+extern "C" int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *counts, const void *query, int q_dtype,
+                                 int32_t B, int32_t h_q, float scaling, void *out, int out_dtype, void *workspace,
+                                 int64_t workspace_bytes, int32_t page_begin, int32_t page_end, int32_t flags,
+                                 float *partial_out, int impl, void *stream) {
+  return decode_attn_core(layer, counts, query, q_dtype, B, h_q, scaling, out, out_dtype, workspace, workspace_bytes,
+                          page_begin, page_end, flags, partial_out, impl, nullptr, stream);
+}
+
+extern "C" int kitty_decode_attn_exchange(const kitty_layer *layer, const kitty_counts *counts, const void *query,
+                                          int q_dtype, int32_t B, int32_t h_q, float scaling, void *out, int out_dtype,
+                                          void *workspace, int64_t workspace_bytes, int32_t page_begin, int32_t page_end,
+                                          int32_t flags, int impl, void *const *peer_buffers, int32_t rank,
+                                          int32_t world, int32_t seq, int32_t *status, void *stream) {
+  if (!out || !peer_buffers || world <= 0 || world > 128 || rank < 0 || rank >= world || seq <= 0) return KITTY_E_BADARG;
+  const int64_t rows = static_cast<int64_t>(B) * h_q;
+  if (rows <= 0 || rows > KITTY_EXCHANGE_MAX_ROWS) return KITTY_E_BADARG;
+  XchgDesc x;
+  x.peers = reinterpret_cast<float *const *>(peer_buffers);
+  kitty_lse_exchange_bytes(rows, world, &x.flag_offset);
+  x.rank = rank;
+  x.world = world;
+  x.seq = seq;
+  x.status = status;
+  return decode_attn_core(layer, counts, query, q_dtype, B, h_q, scaling, out, out_dtype, workspace, workspace_bytes,
+                          page_begin, page_end, flags, nullptr, impl, &x, stream);
 }
 
 extern "C" int kitty_lse_merge(const float *partials, int32_t n_parts, int64_t rows, void *out, int out_dtype,
@@ -212,6 +240,7 @@ extern "C" int kitty_lse_merge(const float *partials, int32_t n_parts, int64_t r
   m.partial_out = nullptr;
   m.work_counter = nullptr;
   m.dyn = nullptr;
+  m.x = XchgDesc{};
   return launch_merge(m, static_cast<cudaStream_t>(stream));
 }
 
@@ -350,6 +379,7 @@ extern "C" int kitty_decode_step(const kitty_layer *layer, const kitty_step_stat
   m.partial_out = nullptr;
   m.work_counter = a.status + 1;
   m.dyn = device_state;
+  m.x = XchgDesc{};
   if (int rc = launch_merge(m, s)) return rc;
   return launch_flush_dyn(*layer, device_state, B, div_mode, s);
 }

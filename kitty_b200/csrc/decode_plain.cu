@@ -9,7 +9,7 @@
 // Dequantisation is `code * scale + min` evaluated in fp32 from the fp16
 // metadata (kernels/kitty_attention.py:162-165, 317-320 of the reference do it in
 // fp16; the difference is inside the stated attention tolerance).
-#include "decode.cuh"
+#include "lse_exchange.cuh"
 
 namespace kitty {
 
@@ -242,6 +242,13 @@ __global__ void __launch_bounds__(128 * MERGE_GROUPS) merge_kernel(MergeArgs a) 
   if (a.work_counter != nullptr && r == 0 && threadIdx.x == 0) *a.work_counter = 0;   // ready for the next call's item hand-out
   if (grp != 0) return;
   if (MERGE_GROUPS == 4) A = (part[0][c] + part[1][c]) + (part[2][c] + part[3][c]);
+  if (a.x.peers != nullptr) {
+    // sequence split: this row's partial goes to every rank, theirs come here, and the result is complete
+    float Ax, Lx;
+    if (!xchg_row(a.x, static_cast<int>(a.rows), static_cast<int>(r), c, A, M, Lsum, Ax, Lx)) return;
+    store_out(a.out, a.out_dtype, r * HD + c, Ax / Lx);
+    return;
+  }
   if (a.partial_out) {
     float *o = a.partial_out + r * PART;
     o[c] = A;
@@ -251,10 +258,7 @@ __global__ void __launch_bounds__(128 * MERGE_GROUPS) merge_kernel(MergeArgs a) 
     }
     return;
   }
-  const float v = A / Lsum;
-  if (a.out_dtype == KITTY_F16) static_cast<__half *>(a.out)[r * HD + c] = __float2half_rn(v);
-  else if (a.out_dtype == KITTY_BF16) static_cast<__nv_bfloat16 *>(a.out)[r * HD + c] = __float2bfloat16_rn(v);
-  else static_cast<float *>(a.out)[r * HD + c] = v;
+  store_out(a.out, a.out_dtype, r * HD + c, A / Lsum);
 }
 
 int launch_decode_plain(const DecodeArgs &a, int items_per_bh, cudaStream_t s) {

@@ -108,6 +108,12 @@ def seq_split_decode(query: torch.Tensor, layer, num_kv_heads: int, scaling: flo
     import torch.distributed as dist
 
     lo, hi = split_pages(n_common_pages, world)[rank]
+    if exchange is not None and partial_fn is None:
+        from .attention import decode_attention
+
+        # one call: this rank's part, then the merge kernel exchanges the partials over peer memory
+        return decode_attention(query, layer, num_kv_heads, scaling, page_begin=lo, page_end=hi,
+                                flags=rank_flags(rank, world), exchange=exchange)
     part = (partial_fn or _cuda_partial)(query, layer, num_kv_heads, scaling, lo, hi, rank_flags(rank, world))
     part = part.contiguous()
     if exchange is not None:

@@ -23,7 +23,7 @@ def _worker(rank, world, port, q_out):
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     import kitty_b200 as kb
-    from kitty_b200.seqsplit import PartialExchange, seq_split_decode
+    from kitty_b200.seqsplit import PartialExchange, rank_flags, seq_split_decode, split_pages
 
     h_kv, h_q, B, L = 4, 28, 1, 32 + 40 * 128 + 50          # the long-context shape: 28 query / 4 KV heads
     cfg = types.SimpleNamespace(num_hidden_layers=1, head_dim=128, num_key_value_heads=h_kv, num_attention_heads=h_q,
@@ -49,6 +49,14 @@ def _worker(rank, world, port, q_out):
                                  exchange=xch)
         torch.cuda.synchronize(dev)
         err_x = max(err_x, (out_x.float() - out.float()).abs().max().item() / out.float().abs().max().item())
+        # and in two calls: partial of this rank's range, then the stand-alone exchange + merge
+        lo, hi = split_pages(lay.PageCount_V, world)[rank]
+        part = torch.empty(B, h_q, 130, dtype=torch.float32, device=dev)
+        kb.decode_attention(q, lay, h_kv, 128 ** -0.5, page_begin=lo, page_end=hi, flags=rank_flags(rank, world),
+                            partial_out=part)
+        out_y = xch.merge(part, q.dtype)
+        torch.cuda.synchronize(dev)
+        err_x = max(err_x, (out_y.float() - out.float()).abs().max().item() / out.float().abs().max().item())
     xch.check()
     q_out.put((rank, err, err_x))
     dist.barrier()

@@ -422,3 +422,36 @@ def test_full_size_131k_group_of_7_properties(kb):
     m, l, acc = ko.attention_partial(qh, K, V, sc)
     assert ko.rel_err(fast[0, 0, h * 7:(h + 1) * 7], acc / l[:, None]) <= ATTN_TOL
     assert kb.workspace_status(lay) == 0
+
+
+def test_attention_with_exchange_in_a_world_of_one(kb):
+    """kitty_decode_attn_exchange with a single rank (its merge kernel publishes to its own buffer and waits for its
+    own flag) returns what kitty_decode_attn returns, for both streaming kernels and on consecutive calls."""
+    import ctypes
+
+    from kitty_b200 import _lib
+
+    for h_kv, h_q in ((2, 8), (1, 7)):
+        B, L = 2, 32 + 128 * 5 + 77
+        cache = kb.KittyCache(_cfg(1, h_kv, h_q), B, L + 64, device=DEV)
+        k, v = make_kv(B, h_kv, L, 128, 21, torch.float16)
+        cache.update(k.to(DEV), v.to(DEV), 0)
+        cache.quantize_prefill(0)
+        lay = cache.kv_cache[0]
+        rows = B * h_q
+        off = ctypes.c_int64(0)
+        nbytes = _lib.lib().kitty_lse_exchange_bytes(rows, 1, ctypes.byref(off))
+        xch = types.SimpleNamespace(rows=rows, rank=0, world=1, seq=0,
+                                    buf=torch.zeros(nbytes // 4, dtype=torch.float32, device=DEV),
+                                    status=torch.zeros(1, dtype=torch.int32, device=DEV))
+        table = torch.tensor([xch.buf.data_ptr()], dtype=torch.int64, device=DEV)
+        xch.peer_table = table.data_ptr()
+        g = torch.Generator().manual_seed(5)
+        for step in range(3):
+            kt, vt = torch.randn(B, h_kv, 1, 128, generator=g).half(), torch.randn(B, h_kv, 1, 128, generator=g).half()
+            cache.update(kt.to(DEV), vt.to(DEV), 0)
+            q = torch.randn(B, h_q, 1, 128, generator=g).half().to(DEV)
+            want = kb.decode_attention(q, lay, h_kv, 0.088)
+            got = kb.decode_attention(q, lay, h_kv, 0.088, exchange=xch)
+            assert torch.equal(got, want), (h_q, step)
+        assert xch.seq == 3 and int(xch.status.item()) == 0
