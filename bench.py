@@ -53,6 +53,7 @@ def parse():
     ap.add_argument("--graph", action="store_true", help="e2e workload: replay the decode step from a CUDA graph")
     ap.add_argument("--e2e-batch", type=int, default=16, help="batch of the e2e workload")
     ap.add_argument("--e2e-steps", type=int, default=256, help="greedy steps of the e2e workload")
+    ap.add_argument("--seq-batch", type=int, default=1, help="seqsplit workload: sequences (the named config has 1)")
     ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
                     help="seqsplit workload: combine the partials with an NCCL all-gather + merge kernel, or inside "
                          "the merge kernel over peer memory")
@@ -359,19 +360,25 @@ def seqsplit_workload(args):
     H_KV, H_Q = 4, 28
     ctx = 131072
     W, K = max(3, args.warmup), args.steps
-    cache = build_cache(kb, 1, ctx, W + K, device, seed=4321)      # same seed: every rank holds the same sequence
-    lay = cache.kv_cache[0]
+    SB = args.seq_batch
+    # NL layers' caches take turns so that every step reads cold pages (NL x 43 MB per sequence > L2) and the steps
+    # can be queued back to back, as the layers of a model are; the same seeds on every rank: same sequences.
+    NL = 8 if SB * 8 * 43 <= 4000 else 4
+    caches = [build_cache(kb, SB, ctx, (W + K) // NL + 2, device, seed=4321 + j) for j in range(NL)]
+    lay = caches[0].kv_cache[0]
     g = torch.Generator(device=device).manual_seed(17)
-    qs = torch.randn(W + K, 1, H_Q, 1, D, generator=g, device=device).to(torch.bfloat16)
-    ks = torch.randn(W + K, 1, H_KV, 1, D, generator=g, device=device).to(torch.bfloat16)
-    vs = torch.randn(W + K, 1, H_KV, 1, D, generator=g, device=device).to(torch.bfloat16)
+    qs = torch.randn(W + K, SB, H_Q, 1, D, generator=g, device=device).to(torch.bfloat16)
+    ks = torch.randn(W + K, SB, H_KV, 1, D, generator=g, device=device).to(torch.bfloat16)
+    vs = torch.randn(W + K, SB, H_KV, 1, D, generator=g, device=device).to(torch.bfloat16)
 
-    xch = PartialExchange(H_Q, device) if (args.exchange == "peer" and world > 1) else None
+    xch = PartialExchange(SB * H_Q, device) if (args.exchange == "peer" and world > 1) else None
 
     def step(i):
+        cache = caches[i % NL]
+        layer = cache.kv_cache[0]
         cache.update(ks[i], vs[i], 0)
-        out = seq_split_decode(qs[i], lay, H_KV, D ** -0.5, rank=rank, world=world, n_common_pages=lay.PageCount_V,
-                               exchange=xch)
+        out = seq_split_decode(qs[i], layer, H_KV, D ** -0.5, rank=rank, world=world,
+                               n_common_pages=layer.PageCount_V, exchange=xch)
         cache.quantize_decode(0)
         return out
 
@@ -382,15 +389,12 @@ def seqsplit_workload(args):
         dist.barrier()
     torch.cuda.synchronize(device)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
-    tot = 0.0
+    e0.record()
     for i in range(K):
-        flush.zero_()                         # evict the cache from L2: one rank's share (5-43 MB) would otherwise stay resident
-        e0.record()
         step(W + i)
-        e1.record()
-        e1.synchronize()
-        tot += e0.elapsed_time(e1)
+    e1.record()
+    e1.synchronize()
+    tot = e0.elapsed_time(e1)
     t = torch.tensor([tot], device=device, dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -398,14 +402,15 @@ def seqsplit_workload(args):
     if xch is not None:
         xch.check()
     if rank == 0:
-        packed = H_KV * (lay.PageCount_K * K_PAGE_BYTES + lay.PageCount_V * V_PAGE_BYTES)
+        packed = SB * H_KV * (lay.PageCount_K * K_PAGE_BYTES + lay.PageCount_V * V_PAGE_BYTES)
         print(json.dumps({"metric": "seqsplit_layer_step_latency", "value": ms * 1e3, "unit": "us", "n_gpus": world,
                           "steps": K, "warmup": W, "higher_is_better": False, "dtype": "f16", "data": "synthetic",
                           "packed_kv_GBps_aggregate": packed / (ms * 1e-3) / 1e9,
-                          "config": {"workload": "1 layer, 28q/4kv heads, batch 1, 131072 cached tokens, sequence split "
-                                                 f"over {world} GPU(s), L2 flushed between steps",
+                          "config": {"workload": f"1 layer, 28q/4kv heads, batch {SB}, 131072 cached tokens, sequence split "
+                                                 f"over {world} GPU(s), {NL} layers' caches in turn (cold pages every step), steps queued "
+                                                 "back to back",
                                      "collective": ("none: partials stored into every rank's buffer over NVLink by the merge "
-                                                    "kernel (kitty_lse_exchange_merge)") if xch is not None else
+                                                    "kernel of the attention call (kitty_decode_attn_exchange)") if xch is not None else
                                      "all_gather of [28,130] fp32 per rank + merge"}}))
     if dist is not None:
         dist.destroy_process_group()

@@ -174,8 +174,7 @@ int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *counts, cons
  *   per layer (capturable): kitty_decode_step(...) = append + attention + merge + flush-if-due.
  *   host, after the token:  advance the counters as kvcache/kitty.py:102-123, 201-234 does
  *                           (kitty_plan_step returns the new counters in state->next).
- * Limits: groups of up to 4 query heads per KV head (the int8 streaming kernel), whole sequence
- * on one GPU, in-kernel channel selection. */
+ * Limits: whole sequence on one GPU, in-kernel channel selection. */
 typedef struct {
   kitty_counts before;   /* state before this step's append                                        */
   kitty_counts after;    /* after the append: what the attention kernels see                       */

@@ -272,7 +272,7 @@ extern "C" int kitty_plan_step(const kitty_layer *layer, const kitty_counts *bef
   const int H = layer->h_kv;
   if (B <= 0 || B > layer->max_bs || H <= 0 || h_q <= 0 || h_q % H != 0) return KITTY_E_BADARG;
   const int G = h_q / H;
-  if (G > 4) return KITTY_E_BADSHAPE;
+  if (G > MAX_GROUP) return KITTY_E_BADSHAPE;
   if (!counts_ok(layer, *before)) return KITTY_E_BADARG;
   kitty_step_state &st = *state;
   st = kitty_step_state{};
@@ -310,13 +310,17 @@ extern "C" int kitty_plan_step(const kitty_layer *layer, const kitty_counts *bef
   st.n_tiles = 1 + static_cast<int>((tk + PAGE - 1) / PAGE);
   st.has_sink = c.Sink_Count > 0 ? 1 : 0;
   st.has_tail = (st.n_tiles - 1 - pv) > 0 ? 1 : 0;
-  const int grid_max = 4 * sm_count();
-  plan_chunks(pv, static_cast<int64_t>(B) * H, grid_max, true, &st.ch, &st.nchunk);
+  // the same plan kitty_decode_attn makes for these counters: int8 kernel for groups of up to 4 heads, fp16 kernel above
+  const bool use_i8 = G <= 4;
+  const int n_gt = use_i8 ? 1 : (G + 7) / 8;
+  const int grid_max = (use_i8 ? 4 : 2) * sm_count();
   plan_edge(st.has_sink, st.has_tail, c, static_cast<int64_t>(B) * H, true, &st.edge_parts, &st.edge_part_tok);
+  const int64_t edge_blocks = use_i8 ? 0 : std::min<int64_t>(static_cast<int64_t>(B) * H * st.edge_parts, grid_max / 2);
+  plan_chunks(pv, static_cast<int64_t>(B) * H * n_gt, grid_max - static_cast<int>(edge_blocks), use_i8, &st.ch, &st.nchunk);
   st.n_slots = st.edge_parts + st.nchunk;
   st.chunk_slot0 = st.edge_parts;
   st.edge_slot = 0;
-  st.n_items = B * H * st.nchunk;
+  st.n_items = B * H * n_gt * st.nchunk;
   st.n_edge = B * H * st.edge_parts;
   if (device_state != nullptr) {
     if ((reinterpret_cast<uintptr_t>(device_state) & 15u) != 0) return KITTY_E_BADARG;
@@ -337,7 +341,7 @@ extern "C" int kitty_decode_step(const kitty_layer *layer, const kitty_step_stat
   const int H = layer->h_kv;
   if (B <= 0 || B > layer->max_bs || B > 65535 || H <= 0 || H > 65535 || h_q <= 0 || h_q % H != 0) return KITTY_E_BADARG;
   const int G = h_q / H;
-  if (G > 4) return KITTY_E_BADSHAPE;
+  if (G > MAX_GROUP) return KITTY_E_BADSHAPE;
   if (kv_dtype < KITTY_F16 || kv_dtype > KITTY_F32 || q_dtype < KITTY_F16 || q_dtype > KITTY_F32 ||
       out_dtype < KITTY_F16 || out_dtype > KITTY_F32)
     return KITTY_E_BADARG;
@@ -365,8 +369,12 @@ extern "C" int kitty_decode_step(const kitty_layer *layer, const kitty_step_stat
   a.status = static_cast<int32_t *>(workspace);
   a.partials = reinterpret_cast<float *>(static_cast<uint8_t *>(workspace) + WS_HEADER);
   a.dyn = device_state;
-  const int grid = 4 * sm_count();                      // fixed: the items are handed out on the device
-  if (int rc = launch_decode_paged_i8(a, 0, 0, grid, s)) return rc;
+  // fixed grids: the item counts are read on the device
+  if (G <= 4) {
+    if (int rc = launch_decode_paged_i8(a, 0, 0, 4 * sm_count(), s)) return rc;
+  } else {
+    if (int rc = launch_decode_paged(a, 0, (G + 7) / 8, 0, 2 * sm_count(), s)) return rc;
+  }
   MergeArgs m;
   m.partials = a.partials;
   m.rows = static_cast<int64_t>(B) * h_q;

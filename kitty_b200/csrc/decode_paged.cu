@@ -43,6 +43,10 @@ struct PagedSmem {
   __align__(16) __half qs[8][QS_ROW];
   __align__(8) unsigned long long bar[PG_WARPS][PG_STAGES];
   uint8_t inv[PG_WARPS][DB];
+  // copy of the device-resident step state (plan, counters, item counts) when the launch carries one
+  DecodePlan dyn_plan;
+  kitty_counts dyn_counts;
+  int dyn_items, dyn_edge;
 };
 static_assert(PG_WARPS * 8 * PART * 4 <= PG_WARPS * PG_STAGES * STAGE_BYTES, "merge buffer overlays the stages");
 
@@ -67,11 +71,28 @@ __device__ __forceinline__ PairSrc pair_src(const DecodeArgs &a, int b, int h, i
 using PagedEdge = EdgeSmem<MAX_GROUP, PG_WARPS, 0>;
 static_assert(sizeof(PagedEdge) <= PG_WARPS * PG_STAGES * STAGE_BYTES, "the edge buffers overlay the stages only");
 
-template <int NGE>
-__global__ void __launch_bounds__(PG_WARPS * 32) decode_paged_kernel(DecodeArgs a, int n_items, int n_gt, int n_edge) {
+// kDyn: the plan, the counters and the item counts come from the device block a.dyn (copied to shared memory once
+// per block) instead of the launch arguments.
+template <int NGE, bool kDyn>
+__global__ void __launch_bounds__(PG_WARPS * 32) decode_paged_kernel(DecodeArgs a, int n_items_arg, int n_gt, int n_edge_arg) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   PagedSmem &sm = *reinterpret_cast<PagedSmem *>(smem_raw);
-  const DecodePlan &P = a.P;
+  if (kDyn && threadIdx.x == 0) {
+    const kitty_step_state &d = *a.dyn;
+    DecodePlan p = a.P;
+    p.pb = d.pb; p.pe = d.pe; p.ch = d.ch; p.nchunk = d.nchunk; p.has_sink = d.has_sink; p.has_tail = d.has_tail;
+    p.n_slots = d.n_slots; p.n_tiles = d.n_tiles; p.chunk_slot0 = d.chunk_slot0; p.edge_slot = d.edge_slot;
+    p.edge_parts = d.edge_parts; p.edge_part_tok = d.edge_part_tok;
+    sm.dyn_plan = p;
+    sm.dyn_counts = d.after;
+    sm.dyn_items = d.n_items;
+    sm.dyn_edge = d.n_edge;
+  }
+  if (kDyn) __syncthreads();
+  const DecodePlan &P = kDyn ? sm.dyn_plan : a.P;
+  const kitty_counts &C = kDyn ? sm.dyn_counts : a.C;
+  const int n_items = kDyn ? sm.dyn_items : n_items_arg;
+  const int n_edge = kDyn ? sm.dyn_edge : n_edge_arg;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int gid = lane >> 2, tig = lane & 3;
   const int H = P.H, G = P.G;
@@ -294,7 +315,7 @@ __global__ void __launch_bounds__(PG_WARPS * 32) decode_paged_kernel(DecodeArgs 
   for (int e = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x); e < n_edge; e += gridDim.x) {
     __syncthreads();     // the previous item's merge buffer / edge buffers are no longer read
     const int ebh = e / P.edge_parts, part = e % P.edge_parts;
-    edge_item<NGE, PG_WARPS>(a, P, a.C, es, ebh / H, ebh % H, part);
+    edge_item<NGE, PG_WARPS>(a, P, C, es, ebh / H, ebh % H, part);
   }
 }
 
@@ -303,15 +324,23 @@ int launch_decode_paged(const DecodeArgs &a, int n_items, int n_gt, int n_edge, 
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return KITTY_E_CUDA;
   if (configured != dev) {
-    if (cudaFuncSetAttribute(decode_paged_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(sizeof(PagedSmem))) != cudaSuccess ||
-        cudaFuncSetAttribute(decode_paged_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(sizeof(PagedSmem))) != cudaSuccess)
+    const int smem = static_cast<int>(sizeof(PagedSmem));
+    if (cudaFuncSetAttribute(decode_paged_kernel<8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+        cudaFuncSetAttribute(decode_paged_kernel<16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+        cudaFuncSetAttribute(decode_paged_kernel<8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+        cudaFuncSetAttribute(decode_paged_kernel<16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return KITTY_E_CUDA;
     configured = dev;
   }
-  if (a.P.G <= 8) decode_paged_kernel<8><<<grid, PG_WARPS * 32, sizeof(PagedSmem), s>>>(a, n_items, n_gt, n_edge);
-  else decode_paged_kernel<16><<<grid, PG_WARPS * 32, sizeof(PagedSmem), s>>>(a, n_items, n_gt, n_edge);
+  const dim3 g(grid), b(PG_WARPS * 32);
+  const size_t sh = sizeof(PagedSmem);
+  if (a.dyn != nullptr) {
+    if (a.P.G <= 8) decode_paged_kernel<8, true><<<g, b, sh, s>>>(a, n_items, n_gt, n_edge);
+    else decode_paged_kernel<16, true><<<g, b, sh, s>>>(a, n_items, n_gt, n_edge);
+  } else {
+    if (a.P.G <= 8) decode_paged_kernel<8, false><<<g, b, sh, s>>>(a, n_items, n_gt, n_edge);
+    else decode_paged_kernel<16, false><<<g, b, sh, s>>>(a, n_items, n_gt, n_edge);
+  }
   return cudaGetLastError() == cudaSuccess ? KITTY_OK : KITTY_E_CUDA;
 }
 

@@ -102,7 +102,9 @@ class KVCache_Layer:
         self.key_states: Optional[torch.Tensor] = None
         self.value_states: Optional[torch.Tensor] = None
         self._c_layer = None
+        self._c_counts = None
         self._workspace: Optional[torch.Tensor] = None
+        self._workspace_need: dict = {}
 
     # -- reference surface ------------------------------------------------- #
     def get_total_length(self) -> int:
@@ -159,7 +161,11 @@ class KVCache_Layer:
         return self._c_layer
 
     def c_counts(self) -> "_lib.KittyCounts":
-        c = _lib.KittyCounts()
+        """struct kitty_counts with the current counters (one struct per layer, refilled on every call: the C
+        entry points copy it before they return)."""
+        c = self._c_counts
+        if c is None:
+            c = self._c_counts = _lib.KittyCounts()
         c.PageCount_K, c.PageCount_V, c.Sink_Count = self.PageCount_K, self.PageCount_V, self.Sink_Count
         c.Q_Buffer_Count_K, c.Q_Buffer_Count_V = self.Q_Buffer_Count_K, self.Q_Buffer_Count_V
         c.Local_Count_V, c.Write_Offset_Local_V, c.reserved = self.Local_Count_V, self.Write_Offset_Local_V, 0
@@ -167,9 +173,12 @@ class KVCache_Layer:
 
     def workspace(self, batch: int, h_q: int) -> torch.Tensor:
         """Zero-initialised scratch for the decode kernels, allocated on first use and kept."""
-        need = _lib.lib().kitty_decode_workspace_bytes(batch, self.H_KV, h_q, self.MAX_PAGE)
-        if need < 0:
-            _lib.check(int(need), "kitty_decode_workspace_bytes")
+        need = self._workspace_need.get((batch, h_q))
+        if need is None:
+            need = _lib.lib().kitty_decode_workspace_bytes(batch, self.H_KV, h_q, self.MAX_PAGE)
+            if need < 0:
+                _lib.check(int(need), "kitty_decode_workspace_bytes")
+            self._workspace_need[(batch, h_q)] = need
         if self._workspace is None or self._workspace.numel() < need:
             self._workspace = torch.zeros(int(need), dtype=torch.uint8, device=self.device)
         return self._workspace

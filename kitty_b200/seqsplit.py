@@ -107,6 +107,10 @@ def seq_split_decode(query: torch.Tensor, layer, num_kv_heads: int, scaling: flo
     partial_fn / merge_fn default to the CUDA library; tests inject host versions."""
     import torch.distributed as dist
 
+    if world == 1 and partial_fn is None:
+        from .attention import decode_attention
+
+        return decode_attention(query, layer, num_kv_heads, scaling)      # nothing to combine
     lo, hi = split_pages(n_common_pages, world)[rank]
     if exchange is not None and partial_fn is None:
         from .attention import decode_attention

@@ -51,11 +51,13 @@ def _inputs(B, h_kv, h_q, step, layer):
     return k, v, q
 
 
-@pytest.mark.parametrize("L,steps", [(10, 60), (32 + 128 * 2 + 120, 24), (32 + 128 + 127, 140)])
-def test_step_state_path_is_bit_identical(kb, L, steps):
+@pytest.mark.parametrize("L,steps,h_kv,h_q", [(10, 60, 2, 8), (32 + 128 * 2 + 120, 24, 2, 8), (32 + 128 + 127, 140, 2, 8),
+                                              (32 + 128 * 2 + 120, 24, 1, 7), (20, 50, 1, 12)])
+def test_step_state_path_is_bit_identical(kb, L, steps, h_kv, h_q):
     """Short prompt (sink and ring still filling), a key flush after 8 steps, and a run long enough for a value
-    flush: same outputs, same buffers, same counters after every step."""
-    B, h_kv, h_q, layers = 3, 2, 8, 2
+    flush: same outputs, same buffers, same counters after every step.  Groups of 4 query heads per KV head take
+    the int8 streaming kernel, 7 and 12 the fp16 one."""
+    B, layers = 3, 2
     cfg = _cfg(layers, h_kv, h_q)
     ref = _prefilled(kb, cfg, B, L, 5, 1024)
     dyn = _prefilled(kb, cfg, B, L, 5, 1024)
@@ -124,10 +126,10 @@ def test_step_state_graph_replay(kb):
 
 
 def test_plan_step_rejects_what_it_cannot_run(kb):
-    cfg = _cfg(1, 1, 8)                      # 8 query heads per KV head: outside the int8 streaming kernel
+    cfg = _cfg(1, 1, 32)                     # 32 query heads per KV head: more than any kernel takes
     cache = kb.get_kvcache_kitty(cfg, 1, 512, device=DEV)
     with pytest.raises(kb.KittyError):
-        cache.plan_step(1, 8)
+        cache.plan_step(1, 32)
     cfg = _cfg(2, 2, 8)
     cache = kb.get_kvcache_kitty(cfg, 1, 512, device=DEV)
     cache.kv_cache[1].Sink_Count = 3         # layers out of step
