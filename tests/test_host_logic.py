@@ -132,3 +132,72 @@ def test_page_pool_hands_out_and_takes_back():
     pool.free([5])
     with pytest.raises(ValueError):
         pool.free([5])                 # already free
+
+
+def _py_step(c):
+    """kvcache/kitty.py:102-123 (append) then :201-234 (flush) on a dict of counters."""
+    a = dict(c)
+    if a["Sink_Count"] < 32:
+        a["Sink_Count"] += 1
+    else:
+        a["Q_Buffer_Count_K"] += 1
+        if a["Local_Count_V"] < 128:
+            a["Local_Count_V"] += 1
+        else:
+            a["Q_Buffer_Count_V"] += 1
+            a["Write_Offset_Local_V"] = (a["Write_Offset_Local_V"] + 1) % 128
+    n = dict(a)
+    fk, fv = n["Q_Buffer_Count_K"] == 128, n["Q_Buffer_Count_V"] == 128
+    if fk:
+        n["PageCount_K"] += 1
+        n["Q_Buffer_Count_K"] = 0
+    if fv:
+        n["PageCount_V"] += 1
+        n["Q_Buffer_Count_V"] = 0
+    return a, n, fk, fv
+
+
+@pytest.mark.parametrize("prompt,h_kv,h_q", [(1, 2, 8), (40, 2, 8), (32 + 128 * 3 + 100, 1, 7)])
+def test_plan_step_follows_the_reference_state_machine(prompt, h_kv, h_q):
+    """kitty_plan_step is host arithmetic (no device needed when no device block is given): its counters after the
+    append and after the flushes must be the reference's, and its item counts must describe the plan."""
+    import ctypes
+
+    from kitty_b200 import _lib
+    from oracle import kitty_oracle as ko
+
+    p = ko.prefill_partition(prompt)
+    c = {"PageCount_K": p["pages_k"], "PageCount_V": p["pages_v"], "Sink_Count": p["sink"],
+         "Q_Buffer_Count_K": p["qbuf_k"], "Q_Buffer_Count_V": p["qbuf_v"], "Local_Count_V": p["local_v"],
+         "Write_Offset_Local_V": 0}
+    L = _lib.KittyLayer()
+    L.max_bs, L.max_page, L.h_kv, L.head_dim, L.d_boost, L.page_size, L.sink_size = 4, 64, h_kv, 128, 32, 128, 32
+    B = 3
+    seen_flush_k = seen_flush_v = 0
+    for _ in range(700):
+        counts = _lib.KittyCounts()
+        for k, v in c.items():
+            setattr(counts, k, v)
+        st = _lib.KittyStepState()
+        rc = _lib.lib().kitty_plan_step(ctypes.byref(L), ctypes.byref(counts), B, h_q, ctypes.byref(st), None, None)
+        assert rc == 0
+        a, n, fk, fv = _py_step(c)
+        assert {k: getattr(st.after, k) for k in c} == a
+        assert {k: getattr(st.next, k) for k in c} == n
+        assert (st.flush_k, st.flush_v) == (int(fk), int(fv))
+        tail = (a["PageCount_K"] - a["PageCount_V"]) * 128 + a["Q_Buffer_Count_K"]
+        assert st.pb == 0 and st.pe == a["PageCount_V"] and st.has_tail == int(tail > 0) and st.has_sink == 1
+        edge_tokens = a["Sink_Count"] + tail
+        assert st.edge_parts == -(-edge_tokens // st.edge_part_tok) and st.edge_part_tok % 64 == 0
+        assert st.n_slots == st.edge_parts + st.nchunk and st.chunk_slot0 == st.edge_parts
+        n_gt = 1 if h_q // h_kv <= 4 else -(-(h_q // h_kv) // 8)
+        assert st.n_items == B * h_kv * n_gt * st.nchunk and st.n_edge == B * h_kv * st.edge_parts
+        assert st.nchunk * st.ch >= a["PageCount_V"] and (st.nchunk == 0) == (a["PageCount_V"] == 0)
+        seen_flush_k += fk
+        seen_flush_v += fv
+        c = n
+    assert seen_flush_k >= 4 and seen_flush_v >= 4
+    bad = _lib.KittyCounts()
+    bad.Sink_Count, bad.Q_Buffer_Count_K = 10, 5          # tokens in the Q-buffer before the sink is full
+    st = _lib.KittyStepState()
+    assert _lib.lib().kitty_plan_step(ctypes.byref(L), ctypes.byref(bad), B, h_q, ctypes.byref(st), None, None) == -1
