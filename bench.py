@@ -519,15 +519,16 @@ def main():
     tokens_per_s = world * B * K / (ms * 1e-3)
 
     # ---------------- end-to-end pass: pinned host inputs, result copied back every step ---------------- #
-    hq = qs[W + K:].cpu().pin_memory()
-    hk = ks[W + K:].cpu().pin_memory()
-    hv = vs[W + K:].cpu().pin_memory()
+    # one pinned buffer per step, [q | k | v] back to back: a single host-to-device copy
+    nq, nk = B * H_Q * D, B * H_KV * D
+    hin = torch.cat([qs[W + K:].reshape(-1, nq), ks[W + K:].reshape(-1, nk), vs[W + K:].reshape(-1, nk)], dim=1).cpu().pin_memory()
     hout = torch.empty(B, 1, H_Q, D, dtype=torch.bfloat16).pin_memory()
 
     def e2e_step(i):
-        q = hq[i].to(device, non_blocking=True)
-        k = hk[i].to(device, non_blocking=True)
-        v = hv[i].to(device, non_blocking=True)
+        x = hin[i].to(device, non_blocking=True)
+        q = x[:nq].view(B, H_Q, 1, D)
+        k = x[nq:nq + nk].view(B, H_KV, 1, D)
+        v = x[nq + nk:].view(B, H_KV, 1, D)
         out = step(q, k, v)
         hout.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()       # the caller reads the result of every step
