@@ -35,6 +35,31 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// ---- programmatic dependent launch ---------------------------------------- //
+// A kernel launched with launch_after() may be scheduled while the kernel before it in the stream is still
+// running, so that its launch latency is hidden; it must call dep_wait() before it touches anything the
+// earlier kernel (or anything before that) wrote — dep_wait() returns once that kernel has completed and its
+// writes are visible.  A kernel that is followed by such a launch calls dep_release() once its blocks are
+// running, which lets the next launch be scheduled early.  Both are no-ops in an ordinary launch.
+__device__ __forceinline__ void dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void dep_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_after(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---- 8 consecutive channels -> fp32 --------------------------------------- //
 template <typename T>
 struct Vec8;

@@ -104,6 +104,7 @@ __global__ void __launch_bounds__(PG_WARPS * 32) decode_paged_kernel(DecodeArgs 
   if (lane < DB) sm.inv[warp][lane] = 0;
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   __syncthreads();
+  dep_release();       // the merge kernel that follows may be scheduled now; it waits for this grid to complete
 
   uint32_t seq = 0;          // page pairs consumed by this warp so far (ring position and parity)
   bool dead = false;         // a bounded wait ran out: stop consuming, keep the barriers uniform

@@ -197,6 +197,7 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
   ws.inv[lane] = 0;
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   __syncthreads();
+  dep_release();       // the merge kernel that follows may be scheduled now; it waits for this grid to complete
 
   uint32_t seq = 0;          // page pairs consumed by this warp so far (mbarrier parity)
   uint32_t edge_phase = 0;   // completed phases of the edge row barrier (block-uniform)

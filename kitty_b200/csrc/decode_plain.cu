@@ -198,6 +198,7 @@ __global__ void __launch_bounds__(128 * MERGE_GROUPS) merge_kernel(MergeArgs a) 
   const int64_t r = blockIdx.x;
   const int c = threadIdx.x & (HD - 1), grp = threadIdx.x >> 7;
   const int lane = threadIdx.x & 31, warp = (threadIdx.x >> 5) & 3;
+  dep_wait();          // launched while the kernel that writes the partials may still be running
   if (a.dyn != nullptr) a.n = a.ns = a.dyn->n_slots;
   const float *base = a.partials + ((r / a.gm) * a.ns * a.gm + r % a.gm) * PART;
   float M = -INFINITY, A = 0.f, Lsum = 0.f;
@@ -269,9 +270,10 @@ int launch_decode_plain(const DecodeArgs &a, int items_per_bh, cudaStream_t s) {
 
 int launch_merge(const MergeArgs &m, cudaStream_t s) {
   if (m.rows == 0) return KITTY_OK;
-  if (m.rows <= 1024) merge_kernel<4><<<static_cast<unsigned>(m.rows), 512, 0, s>>>(m);
-  else merge_kernel<1><<<static_cast<unsigned>(m.rows), 128, 0, s>>>(m);
-  return cudaGetLastError() == cudaSuccess ? KITTY_OK : KITTY_E_CUDA;
+  cudaError_t e;
+  if (m.rows <= 1024) e = launch_after(merge_kernel<4>, dim3(static_cast<unsigned>(m.rows)), dim3(512), 0, s, m);
+  else e = launch_after(merge_kernel<1>, dim3(static_cast<unsigned>(m.rows)), dim3(128), 0, s, m);
+  return (e == cudaSuccess && cudaGetLastError() == cudaSuccess) ? KITTY_OK : KITTY_E_CUDA;
 }
 
 }  // namespace kitty
