@@ -1,5 +1,6 @@
 // Shared constants and small device helpers for the kitty_b200 kernels (sm_100a).
 #pragma once
+#include <cstdlib>
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -56,7 +57,8 @@ inline cudaError_t launch_after(void (*kernel)(KArgs...), dim3 grid, dim3 block,
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
-  cfg.numAttrs = 1;
+  static const bool plain = (getenv("KITTY_PLAIN_LAUNCH") != nullptr);     // diagnostic: ordinary stream order
+  cfg.numAttrs = plain ? 0 : 1;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

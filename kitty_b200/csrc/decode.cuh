@@ -69,8 +69,10 @@ struct MergeArgs {
 };
 
 int launch_decode_plain(const DecodeArgs &a, int items_per_bh, cudaStream_t s);
-int launch_decode_paged(const DecodeArgs &a, int n_items, int n_gt, int n_edge, int grid, cudaStream_t s);
-int launch_decode_paged_i8(const DecodeArgs &a, int n_items, int n_edge, int grid, cudaStream_t s);
+int launch_decode_paged(const DecodeArgs &a, int n_items, int n_gt, int n_edge, int grid, cudaStream_t s,
+                        bool dependent = false);
+int launch_decode_paged_i8(const DecodeArgs &a, int n_items, int n_edge, int grid, cudaStream_t s,
+                           bool dependent = false);   // dependent: programmatic dependent of the kernel before it
 int launch_append_dyn(const kitty_layer &L, const kitty_step_state *dyn, const void *key, const void *value, int dtype,
                       int64_t ksb, int64_t ksh, int64_t vsb, int64_t vsh, int32_t B, cudaStream_t s);
 int launch_flush_dyn(const kitty_layer &L, const kitty_step_state *dyn, int32_t B, int div_mode, cudaStream_t s);

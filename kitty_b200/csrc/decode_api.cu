@@ -371,9 +371,9 @@ extern "C" int kitty_decode_step(const kitty_layer *layer, const kitty_step_stat
   a.dyn = device_state;
   // fixed grids: the item counts are read on the device
   if (G <= 4) {
-    if (int rc = launch_decode_paged_i8(a, 0, 0, 4 * sm_count(), s)) return rc;
+    if (int rc = launch_decode_paged_i8(a, 0, 0, 4 * sm_count(), s, true)) return rc;
   } else {
-    if (int rc = launch_decode_paged(a, 0, (G + 7) / 8, 0, 2 * sm_count(), s)) return rc;
+    if (int rc = launch_decode_paged(a, 0, (G + 7) / 8, 0, 2 * sm_count(), s, true)) return rc;
   }
   MergeArgs m;
   m.partials = a.partials;

@@ -77,6 +77,7 @@ template <int NGE, bool kDyn>
 __global__ void __launch_bounds__(PG_WARPS * 32) decode_paged_kernel(DecodeArgs a, int n_items_arg, int n_gt, int n_edge_arg) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   PagedSmem &sm = *reinterpret_cast<PagedSmem *>(smem_raw);
+  dep_wait();          // step-state chain: launched behind the append kernel, whose rows the edge items read
   if (kDyn && threadIdx.x == 0) {
     const kitty_step_state &d = *a.dyn;
     DecodePlan p = a.P;
@@ -320,7 +321,7 @@ __global__ void __launch_bounds__(PG_WARPS * 32) decode_paged_kernel(DecodeArgs 
   }
 }
 
-int launch_decode_paged(const DecodeArgs &a, int n_items, int n_gt, int n_edge, int grid, cudaStream_t s) {
+int launch_decode_paged(const DecodeArgs &a, int n_items, int n_gt, int n_edge, int grid, cudaStream_t s, bool dependent) {
   static int configured = -1;     // per-process opt-in to > 48 KB dynamic shared memory, done once per device
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return KITTY_E_CUDA;
@@ -335,6 +336,11 @@ int launch_decode_paged(const DecodeArgs &a, int n_items, int n_gt, int n_edge, 
   }
   const dim3 g(grid), b(PG_WARPS * 32);
   const size_t sh = sizeof(PagedSmem);
+  if (dependent && a.dyn != nullptr) {
+    const cudaError_t e = (a.P.G <= 8) ? launch_after(decode_paged_kernel<8, true>, g, b, sh, s, a, n_items, n_gt, n_edge)
+                                       : launch_after(decode_paged_kernel<16, true>, g, b, sh, s, a, n_items, n_gt, n_edge);
+    return (e == cudaSuccess && cudaGetLastError() == cudaSuccess) ? KITTY_OK : KITTY_E_CUDA;
+  }
   if (a.dyn != nullptr) {
     if (a.P.G <= 8) decode_paged_kernel<8, true><<<g, b, sh, s>>>(a, n_items, n_gt, n_edge);
     else decode_paged_kernel<16, true><<<g, b, sh, s>>>(a, n_items, n_gt, n_edge);

@@ -164,6 +164,7 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
   extern __shared__ __align__(128) uint8_t smem_raw[];
   I8Smem &smem = *reinterpret_cast<I8Smem *>(smem_raw);
   I8Main &sm = smem.u.m;
+  dep_wait();          // step-state chain: launched behind the append kernel, whose rows the edge items read
   if (kDyn && threadIdx.x == 0) {
     const kitty_step_state &d = *a.dyn;
     DecodePlan p = a.P;
@@ -537,7 +538,7 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
   }
 }
 
-int launch_decode_paged_i8(const DecodeArgs &a, int n_items, int n_edge, int grid, cudaStream_t s) {
+int launch_decode_paged_i8(const DecodeArgs &a, int n_items, int n_edge, int grid, cudaStream_t s, bool dependent) {
   static int configured = -1;     // per-process opt-in to > 48 KB dynamic shared memory, done once per device
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return KITTY_E_CUDA;
@@ -548,6 +549,12 @@ int launch_decode_paged_i8(const DecodeArgs &a, int n_items, int n_edge, int gri
                              static_cast<int>(sizeof(I8Smem))) != cudaSuccess)
       return KITTY_E_CUDA;
     configured = dev;
+  }
+  if (dependent) {
+    const cudaError_t e = (a.dyn != nullptr)
+        ? launch_after(decode_paged_i8_kernel<true>, dim3(grid), dim3(I8_WARPS * 32), sizeof(I8Smem), s, a, n_items, n_edge)
+        : launch_after(decode_paged_i8_kernel<false>, dim3(grid), dim3(I8_WARPS * 32), sizeof(I8Smem), s, a, n_items, n_edge);
+    return (e == cudaSuccess && cudaGetLastError() == cudaSuccess) ? KITTY_OK : KITTY_E_CUDA;
   }
   if (a.dyn != nullptr)
     decode_paged_i8_kernel<true><<<grid, I8_WARPS * 32, sizeof(I8Smem), s>>>(a, n_items, n_edge);
