@@ -54,6 +54,8 @@ def parse():
     ap.add_argument("--e2e-batch", type=int, default=16, help="batch of the e2e workload")
     ap.add_argument("--e2e-steps", type=int, default=256, help="greedy steps of the e2e workload")
     ap.add_argument("--seq-batch", type=int, default=1, help="seqsplit workload: sequences (the named config has 1)")
+    ap.add_argument("--tail-weight", type=int, default=0,
+                    help="seqsplit workload: packed pages the last rank's tail is counted as when the pages are split")
     ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
                     help="seqsplit workload: combine the partials with an NCCL all-gather + merge kernel, or inside "
                          "the merge kernel over peer memory")
@@ -378,7 +380,7 @@ def seqsplit_workload(args):
         layer = cache.kv_cache[0]
         cache.update(ks[i], vs[i], 0)
         out = seq_split_decode(qs[i], layer, H_KV, D ** -0.5, rank=rank, world=world,
-                               n_common_pages=layer.PageCount_V, exchange=xch)
+                               n_common_pages=layer.PageCount_V, exchange=xch, tail_weight=args.tail_weight)
         cache.quantize_decode(0)
         return out
 
@@ -407,7 +409,7 @@ def seqsplit_workload(args):
                           "steps": K, "warmup": W, "higher_is_better": False, "dtype": "f16", "data": "synthetic",
                           "packed_kv_GBps_aggregate": packed / (ms * 1e-3) / 1e9,
                           "config": {"workload": f"1 layer, 28q/4kv heads, batch {SB}, 131072 cached tokens, sequence split "
-                                                 f"over {world} GPU(s), {NL} layers' caches in turn (cold pages every step), steps queued "
+                                                 f"over {world} GPU(s) (tail weight {args.tail_weight}), {NL} layers' caches in turn (cold pages every step), steps queued "
                                                  "back to back",
                                      "collective": ("none: partials stored into every rank's buffer over NVLink by the merge "
                                                     "kernel of the attention call (kitty_decode_attn_exchange)") if xch is not None else

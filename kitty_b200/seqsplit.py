@@ -19,14 +19,28 @@ from typing import Callable, Optional
 import torch
 
 
-def split_pages(n_pages: int, world: int) -> list[tuple[int, int]]:
-    """Contiguous, balanced page ranges [lo, hi) per rank (earlier ranks get the remainder)."""
-    base, rem = divmod(max(n_pages, 0), world)
+def split_pages(n_pages: int, world: int, tail_weight: int = 0) -> list[tuple[int, int]]:
+    """Contiguous page ranges [lo, hi) per rank.  With tail_weight = 0 the ranges are balanced (earlier ranks get
+    the remainder).  The last rank also reduces the tail of the sequence (fp16 Q-buffers and value ring, up to
+    ~290 tokens per head read with far less parallelism than packed pages); tail_weight says how many packed
+    pages that work is worth, and the last rank gets that many pages fewer (never less than none)."""
+    n_pages, tail_weight = max(n_pages, 0), max(tail_weight, 0)
+
+    def balanced(n, parts):
+        base, rem = divmod(n, parts)
+        return [base + (1 if r < rem else 0) for r in range(parts)]
+
+    if world == 1:
+        return [(0, n_pages)]
+    sizes = balanced(n_pages + tail_weight, world)
+    if sizes[-1] >= tail_weight:
+        sizes[-1] -= tail_weight
+    else:                                          # the tail alone outweighs a share: the last rank takes no pages
+        sizes = balanced(n_pages, world - 1) + [0]
     out, lo = [], 0
-    for r in range(world):
-        hi = lo + base + (1 if r < rem else 0)
-        out.append((lo, hi))
-        lo = hi
+    for sz in sizes:
+        out.append((lo, lo + sz))
+        lo += sz
     return out
 
 
@@ -98,7 +112,7 @@ class PartialExchange:
 
 
 def seq_split_decode(query: torch.Tensor, layer, num_kv_heads: int, scaling: float, *, rank: int, world: int,
-                     n_common_pages: int, group=None, exchange: Optional[PartialExchange] = None,
+                     n_common_pages: int, group=None, exchange: Optional[PartialExchange] = None, tail_weight: int = 0,
                      partial_fn: Optional[Callable] = None, merge_fn: Optional[Callable] = None) -> torch.Tensor:
     """Decode attention of `query` [B, H_Q, 1, D] over a sequence whose common packed pages
     [0, n_common_pages) are split over `world` ranks.  `layer` is this rank's KVCache_Layer (only its own
@@ -111,7 +125,7 @@ def seq_split_decode(query: torch.Tensor, layer, num_kv_heads: int, scaling: flo
         from .attention import decode_attention
 
         return decode_attention(query, layer, num_kv_heads, scaling)      # nothing to combine
-    lo, hi = split_pages(n_common_pages, world)[rank]
+    lo, hi = split_pages(n_common_pages, world, tail_weight)[rank]
     if exchange is not None and partial_fn is None:
         from .attention import decode_attention
 

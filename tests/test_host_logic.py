@@ -201,3 +201,17 @@ def test_plan_step_follows_the_reference_state_machine(prompt, h_kv, h_q):
     bad.Sink_Count, bad.Q_Buffer_Count_K = 10, 5          # tokens in the Q-buffer before the sink is full
     st = _lib.KittyStepState()
     assert _lib.lib().kitty_plan_step(ctypes.byref(L), ctypes.byref(bad), B, h_q, ctypes.byref(st), None, None) == -1
+
+
+def test_split_pages_is_a_contiguous_partition_for_any_tail_weight():
+    from kitty_b200.seqsplit import split_pages
+
+    for n in (0, 1, 7, 10, 100, 1022):
+        for world in (1, 2, 3, 4, 8):
+            for tw in (0, 3, 32, 5000):
+                r = split_pages(n, world, tw)
+                assert len(r) == world and r[0][0] == 0 and r[-1][1] == n
+                assert all(a[1] == b[0] for a, b in zip(r, r[1:])) and all(lo <= hi for lo, hi in r)
+    assert [hi - lo for lo, hi in split_pages(1022, 8)] == [128] * 6 + [127] * 2
+    sizes = [hi - lo for lo, hi in split_pages(1022, 8, 32)]
+    assert sizes[-1] == sizes[0] - 33 and max(sizes[:-1]) - min(sizes[:-1]) <= 1
