@@ -68,8 +68,8 @@ struct Vec8;
 
 template <>
 struct Vec8<__half> {
-  static __device__ __forceinline__ void load(const __half *p, float (&o)[8]) {
-    uint4 v = *reinterpret_cast<const uint4 *>(p);
+  static __device__ __forceinline__ void load(const __half *p, float (&o)[8]) { unpack(*reinterpret_cast<const uint4 *>(p), o); }
+  static __device__ __forceinline__ void unpack(uint4 v, float (&o)[8]) {
     const __half2 *h = reinterpret_cast<const __half2 *>(&v);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -82,8 +82,8 @@ struct Vec8<__half> {
 
 template <>
 struct Vec8<__nv_bfloat16> {
-  static __device__ __forceinline__ void load(const __nv_bfloat16 *p, float (&o)[8]) {
-    uint4 v = *reinterpret_cast<const uint4 *>(p);
+  static __device__ __forceinline__ void load(const __nv_bfloat16 *p, float (&o)[8]) { unpack(*reinterpret_cast<const uint4 *>(p), o); }
+  static __device__ __forceinline__ void unpack(uint4 v, float (&o)[8]) {
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
