@@ -8,7 +8,10 @@ GPU holds `--batch` sequences).  One step = one decode step of that layer
 through the cache object: append the new token's K/V, fused dequant decode
 attention, flush a full Q-buffer if there is one.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference] [--sweep]
+    python bench.py --workload quantize            # bulk prefill quantize/pack throughput
+    python bench.py --workload e2e [--graph]       # Llama-3-8B-shaped decoder, greedy decode with the cache
+    python bench.py --workload seqsplit [--exchange peer] [--seq-batch B]   # 131072-token sequence split over the ranks
 
 Prints one JSON line (rank 0).  `value` is device-timed with the step inputs
 already in HBM; `e2e` runs the same step through the public API from pinned
