@@ -10,7 +10,7 @@ attention, flush a full Q-buffer if there is one.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference] [--sweep]
     python bench.py --workload quantize            # bulk prefill quantize/pack throughput
-    python bench.py --workload e2e [--graph]       # Llama-3-8B-shaped decoder, greedy decode with the cache
+    python bench.py --workload e2e [--no-graph]    # Llama-3-8B-shaped decoder, greedy decode with the cache
     python bench.py --workload seqsplit [--exchange peer] [--seq-batch B]   # 131072-token sequence split over the ranks
 
 Prints one JSON line (rank 0).  `value` is device-timed with the step inputs
@@ -53,7 +53,9 @@ def parse():
                     help="decode (the headline metric), quantize (bulk prefill quantize/pack throughput) or e2e "
                          "(Llama-3-8B-shaped random-init decoder: batch 16, 4096-token prompts, 256 greedy steps)")
     ap.add_argument("--layers", type=int, default=32, help="decoder layers of the e2e workload")
-    ap.add_argument("--graph", action="store_true", help="e2e workload: replay the decode step from a CUDA graph")
+    ap.add_argument("--graph", action=argparse.BooleanOptionalAction, default=True,
+                    help="e2e workload: replay the decode step from a CUDA graph (GraphedDecoder); --no-graph runs the "
+                         "eager patched model")
     ap.add_argument("--e2e-batch", type=int, default=16, help="batch of the e2e workload")
     ap.add_argument("--e2e-steps", type=int, default=256, help="greedy steps of the e2e workload")
     ap.add_argument("--seq-batch", type=int, default=1, help="seqsplit workload: sequences (the named config has 1)")
