@@ -110,6 +110,14 @@ int kitty_prefill_tails(const kitty_layer *layer, const void *key, const void *v
                         int64_t v_stride_h, int64_t v_stride_t, int32_t B, int64_t L, int32_t sink,
                         int32_t qbuf_k, int32_t local_v, int32_t qbuf_v, void *stream);
 
+/* Rotary position embedding of one decode token: q [B, h_q, 128] and k [B, h_kv, 128] (contiguous) to q_out /
+ * k_out of the same shape and type, out = x*cos + rotate_half(x)*sin with every product and the sum rounded to
+ * the data type — bit-identical to the element-wise sequence of the model's attention forward
+ * (models/qwen3/modeling_qwen3.py:222-232), in one launch.  cos / sin: [B or 1, 128] of the same type, rows
+ * cos_stride_b elements apart (0 when all rows share one position). */
+int kitty_rope_qk(const void *q, const void *k, const void *cos, const void *sin, void *q_out, void *k_out, int dtype,
+                  int32_t B, int32_t h_q, int32_t h_kv, int64_t cos_stride_b, void *stream);
+
 /* Decode branch of KittyCache.update (kvcache/kitty.py:101-123): one token per
  * (b, h) goes to the sink, or to Q_Buffer_K and the value ring (the ring's oldest
  * token moving to Q_Buffer_V when the ring is full).  `counts` is the state

@@ -22,7 +22,7 @@ EXPORTS = [
     "kitty_version", "kitty_strerror", "kitty_quant_pack_k", "kitty_quant_pack_v", "kitty_prefill_tails",
     "kitty_append", "kitty_flush", "kitty_decode_workspace_bytes", "kitty_workspace_status", "kitty_decode_attn",
     "kitty_lse_merge", "kitty_decode_attn_static", "kitty_plan_step", "kitty_decode_step",
-    "kitty_lse_exchange_bytes", "kitty_lse_exchange_merge", "kitty_decode_attn_exchange",
+    "kitty_lse_exchange_bytes", "kitty_lse_exchange_merge", "kitty_decode_attn_exchange", "kitty_rope_qk",
 ]
 
 
@@ -108,6 +108,8 @@ def lib() -> C.CDLL:
     L.kitty_decode_attn_exchange.argtypes = [C.POINTER(KittyLayer), C.POINTER(KittyCounts), vp, C.c_int, i32, i32,
                                              C.c_float, vp, C.c_int, vp, i64, i32, i32, i32, C.c_int, vp, i32, i32, i32,
                                              vp, vp]
+    L.kitty_rope_qk.restype = C.c_int
+    L.kitty_rope_qk.argtypes = [vp, vp, vp, vp, vp, vp, C.c_int, i32, i32, i32, i64, vp]
     L.kitty_lse_exchange_bytes.restype = i64
     L.kitty_lse_exchange_bytes.argtypes = [i64, i32, C.POINTER(i64)]
     L.kitty_lse_exchange_merge.restype = C.c_int

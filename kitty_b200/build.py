@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libkitty_b200.so")
-SOURCES = ["quant_pack.cu", "decode_plain.cu", "decode_paged.cu", "decode_paged_i8.cu", "lse_exchange.cu", "decode_api.cu"]
+SOURCES = ["quant_pack.cu", "decode_plain.cu", "decode_paged.cu", "decode_paged_i8.cu", "lse_exchange.cu", "rope.cu", "decode_api.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 

@@ -26,6 +26,29 @@ def _rope(q, k, cos, sin):
     return (q * cos) + (_rotate_half(q) * sin), (k * cos) + (_rotate_half(k) * sin)
 
 
+def rope_decode_token(q: torch.Tensor, k: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor):
+    """Rotary embedding of one decode token in one launch (kitty_rope_qk), bit-identical to `_rope` on the transposed
+    tensors.  q [B, 1, H_Q, D], k [B, 1, H, D] as the projections produce them; cos / sin [B or 1, 1, D].
+    Returns q [B, H_Q, 1, D] and k [B, H, 1, D], contiguous."""
+    from . import _lib
+
+    B, t, h_q, D = q.shape
+    h_kv = k.shape[2]
+    assert t == 1 and D == 128 and q.is_contiguous() and k.is_contiguous()
+    cos2, sin2 = cos.reshape(-1, D), sin.reshape(-1, D)
+    if cos2.dtype != q.dtype:
+        cos2, sin2 = cos2.to(q.dtype), sin2.to(q.dtype)
+    cos2, sin2 = cos2.contiguous(), sin2.contiguous()
+    assert cos2.shape[0] in (1, B) and sin2.shape == cos2.shape
+    q_out = torch.empty((B, h_q, 1, D), dtype=q.dtype, device=q.device)
+    k_out = torch.empty((B, h_kv, 1, D), dtype=k.dtype, device=k.device)
+    rc = _lib.lib().kitty_rope_qk(q.data_ptr(), k.data_ptr(), cos2.data_ptr(), sin2.data_ptr(), q_out.data_ptr(),
+                                  k_out.data_ptr(), _lib.dtype_code(q.dtype), B, h_q, h_kv,
+                                  D if cos2.shape[0] == B and B > 1 else 0, _lib.stream_ptr(q.device))
+    _lib.check(rc, "kitty_rope_qk")
+    return q_out, k_out
+
+
 def kitty_attention_module_forward(self, hidden_states, position_embeddings=None, attention_mask=None,
                                    past_key_values=None, **kwargs):
     """Replacement for `<Model>Attention.forward` (projection layout of Llama / Qwen3)."""
@@ -115,10 +138,9 @@ class GraphedDecoder:
         k = attn.k_proj(hidden_states).view(hidden_shape)
         if getattr(attn, "q_norm", None) is not None:
             q, k = attn.q_norm(q), attn.k_norm(k)
-        q, k = q.transpose(1, 2), k.transpose(1, 2)
-        v = attn.v_proj(hidden_states).view(hidden_shape).transpose(1, 2)
-        q, k = _rope(q, k, cos, sin)
-        out = self.cache.step_layer(attn.layer_idx, k.contiguous(), v.contiguous(), q.contiguous(), attn.scaling)
+        v = attn.v_proj(hidden_states).view(hidden_shape).transpose(1, 2)      # [B, H, 1, D]: contiguous for one token
+        q, k = rope_decode_token(q, k, cos, sin)                                # [B, H_Q, 1, D], [B, H, 1, D]
+        out = self.cache.step_layer(attn.layer_idx, k, v, q, attn.scaling)
         return attn.o_proj(out.reshape(*input_shape, -1))
 
     def _token(self):

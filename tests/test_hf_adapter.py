@@ -87,3 +87,24 @@ def test_greedy_decode_long_prompt_runs_through_flushes():
     lay = cache.kv_cache[1]
     assert cache.get_seq_length(1) == 700 + 139
     assert lay.PageCount_K == (700 + 139 - 32) // 128 and lay.PageCount_V == lay.PageCount_K - 1
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_rope_kernel_is_bit_identical_to_the_elementwise_sequence(dtype):
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from kitty_b200.hf_adapter import _rope, rope_decode_token
+
+    g = torch.Generator().manual_seed(8)
+    B, h_q, h_kv, D = 3, 8, 2, 128
+    q = torch.randn(B, 1, h_q, D, generator=g).to(dtype).cuda()
+    k = torch.randn(B, 1, h_kv, D, generator=g).to(dtype).cuda()
+    for rows in (1, B):                                   # one position for all rows, or one per row
+        ang = torch.rand(rows, 1, D // 2, generator=g) * 6.28
+        ang = torch.cat([ang, ang], dim=-1)
+        cos, sin = ang.cos().to(dtype).cuda(), ang.sin().to(dtype).cuda()
+        want_q, want_k = _rope(q.transpose(1, 2), k.transpose(1, 2), cos, sin)
+        got_q, got_k = rope_decode_token(q, k, cos, sin)
+        assert got_q.is_contiguous() and got_k.is_contiguous()
+        assert torch.equal(got_q, want_q) and torch.equal(got_k, want_k)
