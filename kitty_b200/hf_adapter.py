@@ -58,10 +58,12 @@ def kitty_attention_module_forward(self, hidden_states, position_embeddings=None
     k = self.k_proj(hidden_states).view(hidden_shape)
     if getattr(self, "q_norm", None) is not None:          # Qwen3: RMSNorm on the head dimension
         q, k = self.q_norm(q), self.k_norm(k)
-    q, k = q.transpose(1, 2), k.transpose(1, 2)
     v = self.v_proj(hidden_states).view(hidden_shape).transpose(1, 2)
     cos, sin = position_embeddings
-    q, k = _rope(q, k, cos, sin)
+    if q.shape[1] == 1 and q.is_cuda and q.shape[-1] == 128 and q.is_contiguous() and k.is_contiguous():
+        q, k = rope_decode_token(q, k, cos, sin)          # one launch, same bits as the element-wise sequence
+    else:
+        q, k = _rope(q.transpose(1, 2), k.transpose(1, 2), cos, sin)
     assert past_key_values is not None, "the patched attention needs a KittyCache"
     is_prefill = past_key_values.update(k, v, self.layer_idx)
     if is_prefill:
