@@ -455,3 +455,62 @@ def test_attention_with_exchange_in_a_world_of_one(kb):
             got = kb.decode_attention(q, lay, h_kv, 0.088, exchange=xch)
             assert torch.equal(got, want), (h_q, step)
         assert xch.seq == 3 and int(xch.status.item()) == 0
+
+
+def test_full_size_bulk_quantize_properties(kb):
+    """One layer call of the bulk-quantize workload (65536 tokens x 8 KV heads, bf16, per-channel scales log-uniform
+    in [1, 16]).  Properties that hold for every page at any size: each key page boosts exactly 32 channels whose
+    slots are a permutation of 0..31 and whose scores are the 32 largest; every dequantized element is within half a
+    step (plus the fp16 rounding of scale and minimum) of its input; and a sample of pages is bit-exact with the
+    oracle."""
+    H, T, P = 8, 65536, 512
+    g = torch.Generator(device=DEV).manual_seed(31)
+    sc = torch.exp(torch.rand(1, H, 1, 128, generator=g, device=DEV) * float(np.log(16.0)))
+    k = (torch.randn(1, H, T, 128, generator=g, device=DEV) * sc).to(torch.bfloat16)
+    v = (torch.randn(1, H, T, 128, generator=g, device=DEV) * sc).to(torch.bfloat16)
+    kc, km, vc, vm, pt = _buffers(1, H, P)
+    kb.quantize_pack_k(k, 0, P, pt, 0, kc, km, 128, 32)
+    kb.quantize_pack_v(v, 0, P, pt, 0, vc, vm, 128)
+    shifts = torch.tensor([0, 2, 4, 6], device=DEV, dtype=torch.uint8)
+
+    def fields(b):                                       # [..., n] bytes -> [..., 4n] 2-bit fields, LSB first
+        return ((b.unsqueeze(-1) >> shifts) & 3).flatten(-2)
+
+    # ---- keys ---- //
+    rec = kc.view(P, H, 5248)
+    idx = rec[..., 5120:].to(torch.int64)                                          # [P, H, 128] slot or 32
+    boosted = idx < 32
+    assert bool((boosted.sum(-1) == 32).all())
+    slots = torch.where(boosted, idx, torch.full_like(idx, 99)).sort(-1).values[..., :32]
+    assert bool((slots == torch.arange(32, device=DEV)).all())
+    x = k[0].float().view(H, P, 128, 128).permute(1, 0, 3, 2)                      # [P, H, channel, token]
+    score = x.abs().mean(-1)
+    kth = score.topk(32, dim=-1).values[..., -1:]
+    assert bool((score[boosted].view(P, H, 32) >= kth * (1 - 1e-2)).all())         # scores are rounded to bf16 (spacing 2^-7): ties at the cut
+    lo = fields(rec[..., :4096].reshape(P, H, 128, 32)).float()                    # [P, H, 128, 128]
+    hi_rows = fields(rec[..., 4096:5120].reshape(P, H, 32, 32)).float()            # [P, H, slot, token]
+    hi = torch.gather(hi_rows, 2, idx.clamp(max=31).unsqueeze(-1).expand(-1, -1, -1, 128)) * boosted.unsqueeze(-1)
+    code = lo + 4.0 * hi
+    assert bool((code[~boosted] <= 3).all())
+    scale, mn = km.view(P, H, 128, 2)[..., 0].float().unsqueeze(-1), km.view(P, H, 128, 2)[..., 1].float().unsqueeze(-1)
+    err = (code * scale + mn - x).abs()
+    bound = 0.5 * scale + 16 * 2.0 ** -11 * scale + 2.0 ** -10 * mn.abs() + 1e-6
+    assert bool((err <= bound).all())
+    # ---- values ---- //
+    vcode = fields(vc.view(P, H, 128, 32)).float()                                 # [P, H, token, channel]
+    vscale = vm.view(P, H, 128, 2)[..., 0].float().unsqueeze(-1)
+    vmn = vm.view(P, H, 128, 2)[..., 1].float().unsqueeze(-1)
+    xv = v[0].float().view(H, P, 128, 128).permute(1, 0, 2, 3)
+    verr = (vcode * vscale + vmn - xv).abs()
+    assert bool((verr <= 0.5 * vscale + 4 * 2.0 ** -11 * vscale + 2.0 ** -10 * vmn.abs() + 1e-6).all())
+    # ---- sample pages against the oracle, bit for bit ---- //
+    for p, h in ((0, 0), (137, 3), (511, 7)):
+        page = ko.as_f32(k[0, h, p * 128:(p + 1) * 128].cpu())[None]
+        oi = ko.rank_channels(ko.channel_score(page, "bf16", "exact"), 32, "stable")
+        orec, ometa = ko.quantize_k_pages(page, oi, 32)
+        assert np.array_equal(rec[p, h].cpu().numpy(), orec[0])
+        assert np.array_equal(_f16_bits(km.view(P, H, 128, 2)[p, h]), ometa[0].view(np.int16))
+        vpage = ko.as_f32(v[0, h, p * 128:(p + 1) * 128].cpu())[None]
+        ovrec, ovmeta = ko.quantize_v_pages(vpage)
+        assert np.array_equal(vc.view(P, H, 4096)[p, h].cpu().numpy(), ovrec[0])
+        assert np.array_equal(_f16_bits(vm.view(P, H, 128, 2)[p, h]), ovmeta[0].view(np.int16))
