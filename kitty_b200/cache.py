@@ -42,6 +42,7 @@ class KittyCache(Cache):
         self.selection = selection
         self.div_mode = div_mode
         self._kitty_max_batch, self._kitty_max_length = max_batch_size, max_length
+        self.fuse_eager_steps = True      # patched attention modules use plan_step/step_layer/finish_step for decode tokens
         self._step_dev: Optional[torch.Tensor] = None       # device block of the device-resident decode step
         self._step_host = None
         self.kv_cache: list[KVCache_Layer] = [

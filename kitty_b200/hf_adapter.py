@@ -65,6 +65,16 @@ def kitty_attention_module_forward(self, hidden_states, position_embeddings=None
     else:
         q, k = _rope(q.transpose(1, 2), k.transpose(1, 2), cos, sin)
     assert past_key_values is not None, "the patched attention needs a KittyCache"
+    cache = past_key_values
+    if _fused_step_ok(cache, self.layer_idx, q, k, v):
+        # decode token, all layers in step: one library call per layer (append + attention + flush-if-due from the
+        # device-resident state) instead of three; same bits as the three calls
+        if self.layer_idx == 0:
+            cache.plan_step(q.shape[0], q.shape[1])
+        out = cache.step_layer(self.layer_idx, k, v, q, self.scaling)
+        if self.layer_idx == cache.num_hidden_layers - 1:
+            cache.finish_step()
+        return self.o_proj(out.reshape(*input_shape, -1)), None
     is_prefill = past_key_values.update(k, v, self.layer_idx)
     if is_prefill:
         out = F.scaled_dot_product_attention(q, k, v, is_causal=q.shape[-2] > 1, scale=self.scaling, enable_gqa=True)
@@ -75,6 +85,19 @@ def kitty_attention_module_forward(self, hidden_states, position_embeddings=None
         past_key_values.quantize_decode(self.layer_idx)
     out = out.reshape(*input_shape, -1).contiguous()
     return self.o_proj(out), None
+
+
+def _fused_step_ok(cache, layer_idx: int, q, k, v) -> bool:
+    """The one-call decode step applies when the token is a decode token of a cache that selects channels in the
+    kernel, the layers are visited in order from layer 0, and the tensors have the layout step_layer takes."""
+    if not getattr(cache, "fuse_eager_steps", False) or getattr(cache, "selection", None) != "fused":
+        return False
+    if q.shape[-2] != 1 or not (q.is_contiguous() and k.stride(-1) == 1 and v.stride(-1) == 1 and k.dtype == v.dtype):
+        return False
+    if layer_idx == 0:
+        lay0 = cache.kv_cache[0]
+        return lay0.Sink_Count > 0 and cache._step_host is None and q.shape[1] // lay0.H_KV <= 16
+    return cache._step_host is not None           # a step planned at layer 0 is under way
 
 
 def patch_model(model) -> int:

@@ -108,3 +108,31 @@ def test_rope_kernel_is_bit_identical_to_the_elementwise_sequence(dtype):
         got_q, got_k = rope_decode_token(q, k, cos, sin)
         assert got_q.is_contiguous() and got_k.is_contiguous()
         assert torch.equal(got_q, want_q) and torch.equal(got_k, want_k)
+
+
+@pytest.mark.gpu
+def test_eager_decode_with_one_call_per_layer_equals_three_calls():
+    """The patched attention forward takes decode tokens through plan_step / step_layer / finish_step; switching
+    that off (update -> kitty_attention_forward -> quantize_decode) must give the same tokens and the same cache."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import kitty_b200 as kb
+    from kitty_b200.hf_adapter import greedy_decode, patch_model
+    from tests.helpers import BUFFERS, COUNTERS
+
+    cfg, m = _tiny(torch.bfloat16)
+    m = m.cuda()
+    patch_model(m)
+    ids = torch.randint(0, 1000, (2, 32 + 128 * 2 + 120), device="cuda")
+    outs, caches = [], []
+    for fuse in (True, False):
+        cache = kb.get_kvcache_kitty(cfg, 2, 1024, device="cuda:0")
+        cache.fuse_eager_steps = fuse
+        outs.append(greedy_decode(m, ids, 30, cache))
+        caches.append(cache)
+    assert torch.equal(outs[0], outs[1])
+    for la, lb in zip(caches[0].kv_cache, caches[1].kv_cache):
+        assert [getattr(la, c) for c in COUNTERS] == [getattr(lb, c) for c in COUNTERS]
+        assert la.PageCount_K == 3            # the flush at step 8 went through both paths
+        for n in BUFFERS:
+            assert torch.equal(getattr(la, n), getattr(lb, n)), n
