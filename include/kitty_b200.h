@@ -199,7 +199,8 @@ int kitty_plan_step(const kitty_layer *layer, const kitty_counts *before, int32_
 
 /* One layer's decode step from the device-resident state: kitty_append, kitty_decode_attn
  * (impl 0, whole sequence) and kitty_flush in four launches whose arguments do not depend on the
- * step.  key/value: [B, H, 1, 128] (element strides as for kitty_append); query [B, h_q, 1, 128]
+ * step (streaming, merge and flush kernels are launched as programmatic dependents of the kernel
+ * before them, so their launch latencies overlap).  key/value: [B, H, 1, 128] (element strides as for kitty_append); query [B, h_q, 1, 128]
  * contiguous; out [B, 1, h_q, 128] contiguous; workspace as for kitty_decode_attn. */
 int kitty_decode_step(const kitty_layer *layer, const kitty_step_state *device_state, const void *key,
                       const void *value, int kv_dtype, int64_t k_stride_b, int64_t k_stride_h, int64_t v_stride_b,
