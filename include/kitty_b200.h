@@ -232,9 +232,9 @@ int kitty_decode_step(const kitty_layer *layer, const kitty_step_state *device_s
  * kernels into large shared memory; make that first call outside any stream
  * capture.  A problem whose partials do not fit returns KITTY_E_STATIC_LIMIT
  * before any kernel is launched.  All calls on a device share the one array: the status
- * word is cleared at the start of each call, everything else is overwritten
- * before it is read, and two calls that overlap on the GPU (different streams)
- * race — serialise them. */
+ * word and the item hand-out counter are cleared at the start of each call,
+ * everything else is overwritten before it is read, and two calls that overlap on
+ * the GPU (different streams) race — serialise them. */
 int kitty_decode_attn_static(const kitty_layer *layer, const kitty_counts *counts, const void *query, int q_dtype,
                              int32_t B, int32_t h_q, float scaling, void *out, int out_dtype, int32_t page_begin,
                              int32_t page_end, int32_t flags, float *partial_out, int impl, int32_t *status_out,
@@ -256,10 +256,12 @@ int kitty_lse_merge(const float *partials, int32_t n_parts, int64_t rows, void *
  * the first call.  peer_buffers is a DEVICE array of `world` pointers: entry r is rank r's buffer as
  * mapped in this process.  All ranks call with the same rows/world and the same seq, which starts at 1
  * and grows by one per call.  The kernel stores this rank's partial (fp32 [rows, 130], the partial_out
- * layout) into every rank's buffer, raises a per-row flag, waits at most one second for the other ranks'
- * flags and writes out [rows, 128].  A wait that runs out sets *status (device int32, may be null) and
- * leaves the row unwritten.  rows <= KITTY_EXCHANGE_MAX_ROWS so that every block of the launch is
- * resident (a block waits only for the same row on other GPUs). */
+ * layout) into every rank's buffer, raises a per-row flag, waits at most wait_ns nanoseconds (0: the default
+ * of one second) for the other ranks' flags and writes out [rows, 128].  A wait that runs out sets *status
+ * (device int32, may be null) to 1 and leaves the row unwritten; the kernel returns normally and the context
+ * stays usable (the host reports it as KITTY_E_TIMEOUT once it has read the word).  rows <=
+ * KITTY_EXCHANGE_MAX_ROWS so that every block of the launch is resident (a block waits only for the same row
+ * on other GPUs). */
 #define KITTY_EXCHANGE_MAX_ROWS 1024
 /* kitty_decode_attn of this rank's part of the sequence (page_begin/page_end/flags as there) whose final merge
  * kernel also does the exchange above: one call and one launch fewer per layer than kitty_decode_attn with
@@ -269,10 +271,11 @@ int kitty_decode_attn_exchange(const kitty_layer *layer, const kitty_counts *cou
                                int32_t B, int32_t h_q, float scaling, void *out, int out_dtype, void *workspace,
                                int64_t workspace_bytes, int32_t page_begin, int32_t page_end, int32_t flags, int impl,
                                void *const *peer_buffers, int32_t rank, int32_t world, int32_t seq, int32_t *status,
-                               void *stream);
+                               int64_t wait_ns, void *stream);
 int64_t kitty_lse_exchange_bytes(int64_t rows, int32_t world, int64_t *flag_offset);
 int kitty_lse_exchange_merge(const float *local_partial, int64_t rows, void *const *peer_buffers, int32_t rank,
-                             int32_t world, int32_t seq, void *out, int out_dtype, int32_t *status, void *stream);
+                             int32_t world, int32_t seq, void *out, int out_dtype, int32_t *status, int64_t wait_ns,
+                             void *stream);
 
 #ifdef __cplusplus
 }

@@ -107,13 +107,13 @@ def lib() -> C.CDLL:
     L.kitty_decode_attn_exchange.restype = C.c_int
     L.kitty_decode_attn_exchange.argtypes = [C.POINTER(KittyLayer), C.POINTER(KittyCounts), vp, C.c_int, i32, i32,
                                              C.c_float, vp, C.c_int, vp, i64, i32, i32, i32, C.c_int, vp, i32, i32, i32,
-                                             vp, vp]
+                                             vp, i64, vp]
     L.kitty_rope_qk.restype = C.c_int
     L.kitty_rope_qk.argtypes = [vp, vp, vp, vp, vp, vp, C.c_int, i32, i32, i32, i64, vp]
     L.kitty_lse_exchange_bytes.restype = i64
     L.kitty_lse_exchange_bytes.argtypes = [i64, i32, C.POINTER(i64)]
     L.kitty_lse_exchange_merge.restype = C.c_int
-    L.kitty_lse_exchange_merge.argtypes = [vp, i64, vp, i32, i32, i32, vp, C.c_int, vp, vp]
+    L.kitty_lse_exchange_merge.argtypes = [vp, i64, vp, i32, i32, i32, vp, C.c_int, vp, i64, vp]
     L.kitty_lse_merge.restype = C.c_int
     L.kitty_lse_merge.argtypes = [vp, i32, i64, vp, C.c_int, vp]
     _lib = L

@@ -50,7 +50,8 @@ def decode_attention(query: torch.Tensor, kv_cache: KVCache_Layer, num_kv_heads:
                                                    float(scaling), out_ptr, out_code, ws.data_ptr(), ws.numel(),
                                                    page_begin, page_end, flags, impl, exchange.peer_table,
                                                    exchange.rank, exchange.world, exchange.seq,
-                                                   exchange.status.data_ptr(), _lib.stream_ptr(query.device))
+                                                   exchange.status.data_ptr(), exchange.wait_ns,
+                                                   _lib.stream_ptr(query.device))
         _lib.check(rc, "kitty_decode_attn_exchange")
         return out
     rc = _lib.lib().kitty_decode_attn(layer, counts, query.data_ptr(), _lib.dtype_code(query.dtype), B, H_Q,

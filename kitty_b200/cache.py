@@ -51,6 +51,8 @@ class KittyCache(Cache):
                           PAGE_SIZE=self.page_size, S=self.sink_length, device=device, num_pages=num_pages,
                           page_order=page_order)
             for _ in range(self.num_hidden_layers)]
+        for lay in self.kv_cache[1:]:
+            lay._ws_box = self.kv_cache[0]._ws_box     # one decode workspace for all layers (calls are stream-ordered)
 
     # ------------------------------------------------------------------ #
     def update(self, key_states: torch.Tensor, value_states: torch.Tensor, layer_idx: int,

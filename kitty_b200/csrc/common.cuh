@@ -1,6 +1,6 @@
 // Shared constants and small device helpers for the kitty_b200 kernels (sm_100a).
 #pragma once
-#include <cstdlib>
+#include <atomic>
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -36,6 +36,25 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// ---- once-per-device host set-up ------------------------------------------ //
+// Entry points may be called from several host threads and on several devices.  Set-up that has to
+// happen once per device (function-attribute opt-ins, attribute queries) goes through this helper:
+// `setup` runs with the device current until it has succeeded once on that device.  It must be
+// idempotent, because two threads that arrive together may both run it; nothing else is shared.
+constexpr int MAX_DEVICES = 64;
+struct PerDeviceOnce {
+  std::atomic<int> done[MAX_DEVICES];
+};
+template <typename F>
+inline int per_device_once(PerDeviceOnce &o, F &&setup) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return KITTY_E_CUDA;
+  if (o.done[dev].load(std::memory_order_acquire)) return KITTY_OK;
+  const int rc = setup();
+  if (rc == KITTY_OK) o.done[dev].store(1, std::memory_order_release);
+  return rc;
+}
+
 // ---- programmatic dependent launch ---------------------------------------- //
 // A kernel launched with launch_after() may be scheduled while the kernel before it in the stream is still
 // running, so that its launch latency is hidden; it must call dep_wait() before it touches anything the
@@ -57,8 +76,7 @@ inline cudaError_t launch_after(void (*kernel)(KArgs...), dim3 grid, dim3 block,
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
-  static const bool plain = (getenv("KITTY_PLAIN_LAUNCH") != nullptr);     // diagnostic: ordinary stream order
-  cfg.numAttrs = plain ? 0 : 1;
+  cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

@@ -54,7 +54,10 @@ struct XchgDesc {
   int64_t flag_offset;       // byte offset of the flag area inside an exchange buffer
   int32_t rank, world, seq;
   int32_t *status;           // or null: set non-zero when a wait ran out
+  unsigned long long wait_ns;   // how long a block waits for the other ranks' partials of its row
 };
+
+constexpr unsigned long long XCHG_WAIT_NS_DEFAULT = 1000000000ull;   // 1 s: far beyond any healthy exchange
 
 struct MergeArgs {
   const float *partials;
@@ -77,6 +80,7 @@ int launch_append_dyn(const kitty_layer &L, const kitty_step_state *dyn, const v
                       int64_t ksb, int64_t ksh, int64_t vsb, int64_t vsh, int32_t B, cudaStream_t s);
 int launch_flush_dyn(const kitty_layer &L, const kitty_step_state *dyn, int32_t B, int div_mode, cudaStream_t s);
 int launch_merge(const MergeArgs &m, cudaStream_t s);
+int sm_count();        // multiprocessors of the current device (cached per device)
 
 __device__ __forceinline__ float load_q(const void *q, int dtype, int64_t i) {
   if (dtype == KITTY_F16) return __half2float(static_cast<const __half *>(q)[i]);

@@ -10,17 +10,21 @@ namespace kitty {
 constexpr int64_t WS_HEADER = 256;   // bytes at the start of the workspace: sticky status word, item hand-out counter
 constexpr int PG_WARPS_HOST = 4;     // warps per block of the streaming kernel (pages per chunk come in multiples)
 
-static int sm_count() {
-  static int cached[64] = {0};
+}  // namespace kitty
+
+int kitty::sm_count() {
+  static std::atomic<int> cached[MAX_DEVICES];       // zero-initialised; any thread may fill an entry (same value)
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return 148;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    cached[dev] = n;
+    cached[dev].store(n, std::memory_order_relaxed);
   }
-  return cached[dev];
+  return n;
 }
+
+namespace kitty {
 
 static int chunk_cap(int64_t bh_gt, int grid_max) {
   const int64_t cap = (16LL * grid_max) / std::max<int64_t>(1, bh_gt);
@@ -82,12 +86,13 @@ extern "C" int64_t kitty_decode_workspace_bytes(int32_t B, int32_t h_kv, int32_t
   if (B <= 0 || h_kv <= 0 || h_q <= 0 || h_q % h_kv != 0 || max_pages < 0) return KITTY_E_BADARG;
   const int G = h_q / h_kv;
   if (G > MAX_GROUP) return KITTY_E_BADSHAPE;
-  const int n_gt = (G + 7) / 8;
-  const int grid_max = 4 * sm_count();                        // the larger of the two streaming kernels' resident grids
+  const int64_t grid_max = 4 * sm_count();                    // the larger of the two streaming kernels' resident grids
   const int64_t bh = static_cast<int64_t>(B) * h_kv;
-  int cap = chunk_cap(bh, grid_max);                          // >= the cap any kernel choice uses
-  cap = std::min(cap, std::max(1, (max_pages + PG_WARPS_HOST - 1) / PG_WARPS_HOST));
-  return WS_HEADER + bh * (cap + EDGE_PARTS_MAX) * G * PART * static_cast<int64_t>(sizeof(float));
+  // chunk slots of a call with bh' <= bh rows: bh' * min(chunk_cap(bh'), pages / 4) <= the expression below, which
+  // never decreases with bh — a workspace sized for the largest batch serves every smaller one
+  const int64_t cap_pages = std::min<int64_t>(64, std::max(1, (max_pages + PG_WARPS_HOST - 1) / PG_WARPS_HOST));
+  const int64_t chunk_slots = std::min(bh * cap_pages, std::max(bh, 16 * grid_max));
+  return WS_HEADER + (chunk_slots + bh * EDGE_PARTS_MAX) * G * PART * static_cast<int64_t>(sizeof(float));
 }
 
 static int decode_attn_core(const kitty_layer *layer, const kitty_counts *counts, const void *query, int q_dtype,
@@ -194,7 +199,11 @@ static int decode_attn_core(const kitty_layer *layer, const kitty_counts *counts
   m.work_counter = a.status + 1;
   m.dyn = nullptr;
   m.x = xchg ? *xchg : XchgDesc{};
-  return launch_merge(m, s);
+  const int rc = launch_merge(m, s);
+  // The merge kernel is what leaves the item hand-out counter at zero for the next call.  If it could not be
+  // launched, zero the counter in stream order so that a failed call cannot poison the workspace.
+  if (rc != KITTY_OK) cudaMemsetAsync(a.status + 1, 0, sizeof(int32_t), s);
+  return rc;
 }
 
 extern "C" int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *counts, const void *query, int q_dtype,
@@ -209,8 +218,10 @@ extern "C" int kitty_decode_attn_exchange(const kitty_layer *layer, const kitty_
                                           int q_dtype, int32_t B, int32_t h_q, float scaling, void *out, int out_dtype,
                                           void *workspace, int64_t workspace_bytes, int32_t page_begin, int32_t page_end,
                                           int32_t flags, int impl, void *const *peer_buffers, int32_t rank,
-                                          int32_t world, int32_t seq, int32_t *status, void *stream) {
-  if (!out || !peer_buffers || world <= 0 || world > 128 || rank < 0 || rank >= world || seq <= 0) return KITTY_E_BADARG;
+                                          int32_t world, int32_t seq, int32_t *status, int64_t wait_ns,
+                                          void *stream) {
+  if (!out || !peer_buffers || world <= 0 || world > 128 || rank < 0 || rank >= world || seq <= 0 || wait_ns < 0)
+    return KITTY_E_BADARG;
   const int64_t rows = static_cast<int64_t>(B) * h_q;
   if (rows <= 0 || rows > KITTY_EXCHANGE_MAX_ROWS) return KITTY_E_BADARG;
   XchgDesc x;
@@ -220,6 +231,7 @@ extern "C" int kitty_decode_attn_exchange(const kitty_layer *layer, const kitty_
   x.world = world;
   x.seq = seq;
   x.status = status;
+  x.wait_ns = wait_ns > 0 ? static_cast<unsigned long long>(wait_ns) : XCHG_WAIT_NS_DEFAULT;
   return decode_attn_core(layer, counts, query, q_dtype, B, h_q, scaling, out, out_dtype, workspace, workspace_bytes,
                           page_begin, page_end, flags, nullptr, impl, &x, stream);
 }
@@ -427,22 +439,22 @@ extern "C" const char *kitty_strerror(int status) {
 static __device__ __align__(256) unsigned char g_static_scratch[KITTY_STATIC_SCRATCH_BYTES];
 
 static void *static_scratch_ptr(int *rc) {
-  static void *cached[64] = {nullptr};
+  static std::atomic<void *> cached[MAX_DEVICES];    // zero-initialised; any thread may fill an entry (same value)
   int dev = 0;
   *rc = KITTY_OK;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
     *rc = KITTY_E_CUDA;
     return nullptr;
   }
-  if (cached[dev] == nullptr) {
-    void *p = nullptr;
+  void *p = cached[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
     if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) {
       *rc = KITTY_E_CUDA;
       return nullptr;
     }
-    cached[dev] = p;
+    cached[dev].store(p, std::memory_order_release);
   }
-  return cached[dev];
+  return p;
 }
 
 extern "C" int kitty_decode_attn_static(const kitty_layer *layer, const kitty_counts *counts, const void *query,
@@ -453,8 +465,10 @@ extern "C" int kitty_decode_attn_static(const kitty_layer *layer, const kitty_co
   void *ws = static_scratch_ptr(&rc);
   if (rc != KITTY_OK) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  // the status word is the one thing that has to start at zero; the partial slots are written before they are read
-  if (cudaMemsetAsync(ws, 0, sizeof(int32_t), s) != cudaSuccess) return KITTY_E_CUDA;
+  // Two words have to start at zero: the status word and the item hand-out counter behind it (an earlier call on
+  // this device that failed half-way may have left the counter dirty, and no caller can reach the array to
+  // repair it).  The partial slots are written before they are read.
+  if (cudaMemsetAsync(ws, 0, 2 * sizeof(int32_t), s) != cudaSuccess) return KITTY_E_CUDA;
   rc = kitty_decode_attn(layer, counts, query, q_dtype, B, h_q, scaling, out, out_dtype, ws,
                          static_cast<int64_t>(KITTY_STATIC_SCRATCH_BYTES), page_begin, page_end, flags, partial_out, impl,
                          stream);

@@ -322,18 +322,16 @@ __global__ void __launch_bounds__(PG_WARPS * 32) decode_paged_kernel(DecodeArgs 
 }
 
 int launch_decode_paged(const DecodeArgs &a, int n_items, int n_gt, int n_edge, int grid, cudaStream_t s, bool dependent) {
-  static int configured = -1;     // per-process opt-in to > 48 KB dynamic shared memory, done once per device
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return KITTY_E_CUDA;
-  if (configured != dev) {
-    const int smem = static_cast<int>(sizeof(PagedSmem));
-    if (cudaFuncSetAttribute(decode_paged_kernel<8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
-        cudaFuncSetAttribute(decode_paged_kernel<16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
-        cudaFuncSetAttribute(decode_paged_kernel<8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
-        cudaFuncSetAttribute(decode_paged_kernel<16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return KITTY_E_CUDA;
-    configured = dev;
-  }
+  static PerDeviceOnce once;      // opt-in to > 48 KB dynamic shared memory, once per device
+  if (int rc = per_device_once(once, [] {
+        const int smem = static_cast<int>(sizeof(PagedSmem));
+        return (cudaFuncSetAttribute(decode_paged_kernel<8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess &&
+                cudaFuncSetAttribute(decode_paged_kernel<16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess &&
+                cudaFuncSetAttribute(decode_paged_kernel<8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess &&
+                cudaFuncSetAttribute(decode_paged_kernel<16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess)
+                   ? KITTY_OK : KITTY_E_CUDA;
+      }))
+    return rc;
   const dim3 g(grid), b(PG_WARPS * 32);
   const size_t sh = sizeof(PagedSmem);
   if (dependent && a.dyn != nullptr) {

@@ -539,17 +539,14 @@ __global__ void __launch_bounds__(I8_WARPS * 32, 4) decode_paged_i8_kernel(Decod
 }
 
 int launch_decode_paged_i8(const DecodeArgs &a, int n_items, int n_edge, int grid, cudaStream_t s, bool dependent) {
-  static int configured = -1;     // per-process opt-in to > 48 KB dynamic shared memory, done once per device
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return KITTY_E_CUDA;
-  if (configured != dev) {
-    if (cudaFuncSetAttribute(decode_paged_i8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(sizeof(I8Smem))) != cudaSuccess ||
-        cudaFuncSetAttribute(decode_paged_i8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(sizeof(I8Smem))) != cudaSuccess)
-      return KITTY_E_CUDA;
-    configured = dev;
-  }
+  static PerDeviceOnce once;      // opt-in to > 48 KB dynamic shared memory, once per device
+  if (int rc = per_device_once(once, [] {
+        const int smem = static_cast<int>(sizeof(I8Smem));
+        return (cudaFuncSetAttribute(decode_paged_i8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess &&
+                cudaFuncSetAttribute(decode_paged_i8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess)
+                   ? KITTY_OK : KITTY_E_CUDA;
+      }))
+    return rc;
   if (dependent) {
     const cudaError_t e = (a.dyn != nullptr)
         ? launch_after(decode_paged_i8_kernel<true>, dim3(grid), dim3(I8_WARPS * 32), sizeof(I8Smem), s, a, n_items, n_edge)

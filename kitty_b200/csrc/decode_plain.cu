@@ -9,6 +9,8 @@
 // Dequantisation is `code * scale + min` evaluated in fp32 from the fp16
 // metadata (kernels/kitty_attention.py:162-165, 317-320 of the reference do it in
 // fp16; the difference is inside the stated attention tolerance).
+#include <algorithm>
+
 #include "lse_exchange.cuh"
 
 namespace kitty {
@@ -272,7 +274,11 @@ int launch_decode_plain(const DecodeArgs &a, int items_per_bh, cudaStream_t s) {
 int launch_merge(const MergeArgs &m, cudaStream_t s) {
   if (m.rows == 0) return KITTY_OK;
   cudaError_t e;
-  if (m.rows <= 1024) e = launch_after(merge_kernel<4>, dim3(static_cast<unsigned>(m.rows)), dim3(512), 0, s, m);
+  // With a peer exchange every block waits for the block of the same row on the other GPUs, so all blocks of the
+  // launch have to be resident at once: 512-thread blocks fit four per multiprocessor, 128-thread blocks sixteen.
+  const int64_t wide_max = m.x.peers != nullptr ? std::min<int64_t>(1024, 4LL * sm_count()) : 1024;
+  if (m.x.peers != nullptr && m.rows > 16LL * sm_count()) return KITTY_E_BADARG;
+  if (m.rows <= wide_max) e = launch_after(merge_kernel<4>, dim3(static_cast<unsigned>(m.rows)), dim3(512), 0, s, m);
   else e = launch_after(merge_kernel<1>, dim3(static_cast<unsigned>(m.rows)), dim3(128), 0, s, m);
   return (e == cudaSuccess && cudaGetLastError() == cudaSuccess) ? KITTY_OK : KITTY_E_CUDA;
 }

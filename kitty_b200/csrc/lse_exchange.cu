@@ -40,11 +40,11 @@ extern "C" int64_t kitty_lse_exchange_bytes(int64_t rows, int32_t world, int64_t
 
 extern "C" int kitty_lse_exchange_merge(const float *local_partial, int64_t rows, void *const *peer_buffers,
                                         int32_t rank, int32_t world, int32_t seq, void *out, int out_dtype,
-                                        int32_t *status, void *stream) {
+                                        int32_t *status, int64_t wait_ns, void *stream) {
   if (!local_partial || !peer_buffers || !out) return KITTY_E_BADARG;
   if (rows <= 0 || rows > KITTY_EXCHANGE_MAX_ROWS || world <= 0 || world > 128 || rank < 0 || rank >= world || seq <= 0)
     return KITTY_E_BADARG;
-  if (out_dtype < KITTY_F16 || out_dtype > KITTY_F32) return KITTY_E_BADARG;
+  if (out_dtype < KITTY_F16 || out_dtype > KITTY_F32 || wait_ns < 0) return KITTY_E_BADARG;
   XchgArgs a;
   a.local = local_partial;
   a.x.peers = reinterpret_cast<float *const *>(peer_buffers);
@@ -53,6 +53,7 @@ extern "C" int kitty_lse_exchange_merge(const float *local_partial, int64_t rows
   a.x.world = world;
   a.x.seq = seq;
   a.x.status = status;
+  a.x.wait_ns = wait_ns > 0 ? static_cast<unsigned long long>(wait_ns) : XCHG_WAIT_NS_DEFAULT;
   a.rows = static_cast<int32_t>(rows);
   a.out = out;
   a.out_dtype = out_dtype;

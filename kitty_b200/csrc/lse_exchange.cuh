@@ -9,14 +9,13 @@
 // rank's flag of that call.  A block only waits for the block of the same row on the other GPUs, never for a
 // block of its own GPU; the row count is capped so that every block of a launch is resident at once and no
 // waiting block can keep a needed one from starting.  No multicast, no TMA: ordinary stores, a system-scope
-// fence, volatile loads.  Every wait is bounded by time and reports through a status word.
+// fence, volatile loads.  Every wait is bounded by time (XchgDesc::wait_ns) and reports through a status word.
 #pragma once
 
 #include "decode.cuh"
 
 namespace kitty {
 
-constexpr unsigned long long XCHG_WAIT_NS = 1000000000ull;   // 1 s: far beyond any healthy exchange
 
 __device__ __forceinline__ unsigned long long xchg_ns() {
   unsigned long long t;
@@ -53,7 +52,7 @@ __device__ __forceinline__ bool xchg_row(const XchgDesc &x, int rows, int r, int
     const int64_t slot = (static_cast<int64_t>(par) * x.world + c) * rows + r;
     const unsigned long long t0 = xchg_ns();
     while (mine[slot] != x.seq) {
-      if (xchg_ns() - t0 > XCHG_WAIT_NS) {
+      if (xchg_ns() - t0 > x.wait_ns) {
         xok_s = 0;
         if (x.status != nullptr) atomicExch(x.status, 1);
         break;

@@ -49,9 +49,30 @@ def rope_decode_token(q: torch.Tensor, k: torch.Tensor, cos: torch.Tensor, sin: 
     return q_out, k_out
 
 
+def _prefill_attention(q, k, v, attention_mask, scaling):
+    """Prompt attention on the full-precision K/V (models/qwen3/modeling_qwen3.py:228-242 hands the mask to the
+    attention interface).  attention_mask: None (plain causal), or the model's 4-D mask — boolean (True = attend)
+    or additive float — covering [B, 1, L, L]; a padded batch arrives that way."""
+    if attention_mask is None:
+        return F.scaled_dot_product_attention(q, k, v, is_causal=q.shape[-2] > 1, scale=scaling, enable_gqa=True)
+    if attention_mask.dim() != 4:
+        raise ValueError("the patched attention expects the model's 4-D attention mask, got shape "
+                         f"{tuple(attention_mask.shape)}")
+    mask = attention_mask[..., : k.shape[-2]]
+    if mask.dtype != torch.bool:
+        mask = mask.to(q.dtype)
+    return F.scaled_dot_product_attention(q, k, v, attn_mask=mask, is_causal=False, scale=scaling, enable_gqa=True)
+
+
 def kitty_attention_module_forward(self, hidden_states, position_embeddings=None, attention_mask=None,
-                                   past_key_values=None, **kwargs):
-    """Replacement for `<Model>Attention.forward` (projection layout of Llama / Qwen3)."""
+                                   past_key_values=None, past_key_value=None, **kwargs):
+    """Replacement for `<Model>Attention.forward` (projection layout of Llama / Qwen3).  The cache may arrive as
+    `past_key_values` or, as in the reference's signature and older transformers, `past_key_value`.  Decode tokens
+    ignore the mask, as the reference's decode path does (kernels/kitty_attention.py:403-526 takes none)."""
+    if past_key_values is None:
+        past_key_values = past_key_value
+    if getattr(self, "sliding_window", None) is not None:
+        raise NotImplementedError("the Kitty cache keeps every token: sliding-window attention layers are not supported")
     input_shape = hidden_states.shape[:-1]
     hidden_shape = (*input_shape, -1, self.head_dim)
     q = self.q_proj(hidden_states).view(hidden_shape)
@@ -77,8 +98,7 @@ def kitty_attention_module_forward(self, hidden_states, position_embeddings=None
         return self.o_proj(out.reshape(*input_shape, -1)), None
     is_prefill = past_key_values.update(k, v, self.layer_idx)
     if is_prefill:
-        out = F.scaled_dot_product_attention(q, k, v, is_causal=q.shape[-2] > 1, scale=self.scaling, enable_gqa=True)
-        out = out.transpose(1, 2)
+        out = _prefill_attention(q, k, v, attention_mask, self.scaling).transpose(1, 2)
         past_key_values.quantize_prefill(self.layer_idx)
     else:
         out, _ = kitty_attention_forward(self, q.contiguous(), past_key_values.kv_cache[self.layer_idx], self.scaling)

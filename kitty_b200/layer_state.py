@@ -103,7 +103,9 @@ class KVCache_Layer:
         self.value_states: Optional[torch.Tensor] = None
         self._c_layer = None
         self._c_counts = None
-        self._workspace: Optional[torch.Tensor] = None
+        # scratch of the decode kernels, in a one-element box so that the layers of a cache can share one buffer
+        # (their calls are serialised on the stream): KittyCache points every layer at the same box
+        self._ws_box: list = [None]
         self._workspace_need: dict = {}
 
     # -- reference surface ------------------------------------------------- #
@@ -180,5 +182,9 @@ class KVCache_Layer:
                 _lib.check(int(need), "kitty_decode_workspace_bytes")
             self._workspace_need[(batch, h_q)] = need
         if self._workspace is None or self._workspace.numel() < need:
-            self._workspace = torch.zeros(int(need), dtype=torch.uint8, device=self.device)
+            self._ws_box[0] = torch.zeros(int(need), dtype=torch.uint8, device=self.device)
         return self._workspace
+
+    @property
+    def _workspace(self) -> Optional[torch.Tensor]:
+        return self._ws_box[0]

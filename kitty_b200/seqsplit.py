@@ -68,7 +68,7 @@ class PartialExchange:
     """Peer-addressable buffers for kitty_lse_exchange_merge: one symmetric-memory allocation per rank, every
     rank's copy mapped into every process (torch.distributed._symmetric_memory), zeroed once.  `rows` = B * H_Q."""
 
-    def __init__(self, rows: int, device, group=None):
+    def __init__(self, rows: int, device, group=None, wait_ns: int = 0):
         import ctypes
 
         import torch.distributed as dist
@@ -88,8 +88,26 @@ class PartialExchange:
         self.peer_table = int(self.handle.buffer_ptrs_dev)        # device array of `world` buffer addresses
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.seq = 0
+        self.wait_ns = int(wait_ns)                               # 0: the library's default limit (1 s)
         torch.cuda.synchronize(device)
         dist.barrier(group)                                       # every buffer is zero before anyone writes
+
+    @classmethod
+    def from_buffers(cls, rows: int, rank: int, buffers: list, wait_ns: int = 0) -> "PartialExchange":
+        """An exchange over buffers the caller already holds (`buffers[r]` = rank r's zero-filled exchange buffer as
+        addressable from this process, each of kitty_lse_exchange_bytes(rows, len(buffers)) bytes).  No process
+        group is touched."""
+        self = cls.__new__(cls)
+        self.rank, self.world, self.rows = rank, len(buffers), rows
+        self.buf, self.handle = buffers[rank], None
+        self._buffers = list(buffers)
+        dev = buffers[rank].device
+        self._table = torch.tensor([b.data_ptr() for b in buffers], dtype=torch.int64, device=dev)
+        self.peer_table = self._table.data_ptr()
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.seq = 0
+        self.wait_ns = int(wait_ns)
+        return self
 
     def merge(self, part: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         """part: this rank's fp32 [B, H_Q, 130] partial.  Returns [B, 1, H_Q, 128] (identical on every rank)."""
@@ -101,14 +119,17 @@ class PartialExchange:
         self.seq += 1
         rc = _lib.lib().kitty_lse_exchange_merge(part.data_ptr(), self.rows, self.peer_table, self.rank, self.world,
                                                  self.seq, out.data_ptr(), _lib.dtype_code(out_dtype),
-                                                 self.status.data_ptr(), _lib.stream_ptr(part.device))
+                                                 self.status.data_ptr(), self.wait_ns, _lib.stream_ptr(part.device))
         _lib.check(rc, "kitty_lse_exchange_merge")
         return out
 
     def check(self) -> None:
         """Synchronise and raise if a bounded wait of an earlier merge ran out."""
+        from . import _lib
+
         if int(self.status.item()) != 0:
-            raise RuntimeError("kitty_lse_exchange_merge: a peer's partial did not arrive within the wait limit")
+            raise _lib.KittyError(_lib.KITTY_E_TIMEOUT, "kitty_lse_exchange_merge (a peer's partial did not arrive "
+                                                        "within the wait limit; rows it was needed for are unwritten)")
 
 
 def seq_split_decode(query: torch.Tensor, layer, num_kv_heads: int, scaling: float, *, rank: int, world: int,
@@ -138,7 +159,14 @@ def seq_split_decode(query: torch.Tensor, layer, num_kv_heads: int, scaling: flo
         return exchange.merge(part, query.dtype)
     flat = torch.empty((world * part.shape[0],) + tuple(part.shape[1:]), dtype=part.dtype, device=part.device)
     if world > 1:
-        dist.all_gather_into_tensor(flat, part, group=group)      # rank r's rows land at [r*B, (r+1)*B)
+        try:
+            dist.all_gather_into_tensor(flat, part, group=group)      # rank r's rows land at [r*B, (r+1)*B)
+        except RuntimeError as e:
+            # a rank that never contributed its partial: the collective ends with the process group's timeout
+            from . import _lib
+
+            raise _lib.KittyError(_lib.KITTY_E_TIMEOUT, "sequence-split all-gather (a rank's partial did not arrive: "
+                                  f"{str(e).splitlines()[0][:160]})") from e
     else:
         flat.copy_(part)
     parts = flat.view((world,) + tuple(part.shape))

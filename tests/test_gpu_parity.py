@@ -375,13 +375,13 @@ def test_exchange_merge_single_rank_equals_lse_merge(kb):
         part[..., 129] = part[..., 129].abs() + 0.5
         out = torch.empty(1, 1, rows, 128, dtype=torch.float32, device=DEV)
         rc = _lib.lib().kitty_lse_exchange_merge(part.data_ptr(), rows, table.data_ptr(), 0, 1, seq, out.data_ptr(),
-                                                 _lib.KITTY_F32, status.data_ptr(), _lib.stream_ptr(torch.device(DEV)))
+                                                 _lib.KITTY_F32, status.data_ptr(), 0, _lib.stream_ptr(torch.device(DEV)))
         assert rc == 0
         want = kb.lse_merge(part.view(1, 1, rows, 130).contiguous(), torch.float32)
         assert torch.allclose(out, want, rtol=1e-6, atol=0)
     assert int(status.item()) == 0
     assert _lib.lib().kitty_lse_exchange_merge(part.data_ptr(), 2000, table.data_ptr(), 0, 1, 9, out.data_ptr(),
-                                               _lib.KITTY_F32, None, None) == _lib.KITTY_E_BADARG
+                                               _lib.KITTY_F32, None, 0, None) == _lib.KITTY_E_BADARG
 
 
 def test_full_size_131k_group_of_7_properties(kb):
@@ -441,7 +441,7 @@ def test_attention_with_exchange_in_a_world_of_one(kb):
         rows = B * h_q
         off = ctypes.c_int64(0)
         nbytes = _lib.lib().kitty_lse_exchange_bytes(rows, 1, ctypes.byref(off))
-        xch = types.SimpleNamespace(rows=rows, rank=0, world=1, seq=0,
+        xch = types.SimpleNamespace(rows=rows, rank=0, world=1, seq=0, wait_ns=0,
                                     buf=torch.zeros(nbytes // 4, dtype=torch.float32, device=DEV),
                                     status=torch.zeros(1, dtype=torch.int32, device=DEV))
         table = torch.tensor([xch.buf.data_ptr()], dtype=torch.int64, device=DEV)
@@ -461,8 +461,8 @@ def test_full_size_bulk_quantize_properties(kb):
     """One layer call of the bulk-quantize workload (65536 tokens x 8 KV heads, bf16, per-channel scales log-uniform
     in [1, 16]).  Properties that hold for every page at any size: each key page boosts exactly 32 channels whose
     slots are a permutation of 0..31 and whose scores are the 32 largest; every dequantized element is within half a
-    step (plus the fp16 rounding of scale and minimum) of its input; and a sample of pages is bit-exact with the
-    oracle."""
+    step (plus the fp16 rounding of scale and minimum) of its input; and all 4096 page-heads of the call, keys and
+    values, are bit-exact with the oracle."""
     H, T, P = 8, 65536, 512
     g = torch.Generator(device=DEV).manual_seed(31)
     sc = torch.exp(torch.rand(1, H, 1, 128, generator=g, device=DEV) * float(np.log(16.0)))
@@ -503,14 +503,15 @@ def test_full_size_bulk_quantize_properties(kb):
     xv = v[0].float().view(H, P, 128, 128).permute(1, 0, 2, 3)
     verr = (vcode * vscale + vmn - xv).abs()
     assert bool((verr <= 0.5 * vscale + 4 * 2.0 ** -11 * vscale + 2.0 ** -10 * vmn.abs() + 1e-6).all())
-    # ---- sample pages against the oracle, bit for bit ---- //
-    for p, h in ((0, 0), (137, 3), (511, 7)):
-        page = ko.as_f32(k[0, h, p * 128:(p + 1) * 128].cpu())[None]
-        oi = ko.rank_channels(ko.channel_score(page, "bf16", "exact"), 32, "stable")
-        orec, ometa = ko.quantize_k_pages(page, oi, 32)
-        assert np.array_equal(rec[p, h].cpu().numpy(), orec[0])
-        assert np.array_equal(_f16_bits(km.view(P, H, 128, 2)[p, h]), ometa[0].view(np.int16))
-        vpage = ko.as_f32(v[0, h, p * 128:(p + 1) * 128].cpu())[None]
-        ovrec, ovmeta = ko.quantize_v_pages(vpage)
-        assert np.array_equal(vc.view(P, H, 4096)[p, h].cpu().numpy(), ovrec[0])
-        assert np.array_equal(_f16_bits(vm.view(P, H, 128, 2)[p, h]), ovmeta[0].view(np.int16))
+    # ---- every page-head of the call against the oracle, bit for bit: codes, high plane, index bytes, fp16 (scale, min) ---- //
+    kp = ko.as_f32(k[0].cpu()).reshape(H, P, 128, 128)
+    oi = ko.rank_channels(ko.channel_score(kp, "bf16", "exact"), 32, "stable")
+    orec, ometa = ko.quantize_k_pages(kp.reshape(-1, 128, 128), oi.reshape(-1, 128), 32)
+    orec, ometa = orec.reshape(H, P, 5248).transpose(1, 0, 2), ometa.reshape(H, P, 128, 2).transpose(1, 0, 2, 3)
+    assert np.array_equal(rec.cpu().numpy(), orec)
+    assert np.array_equal(_f16_bits(km.view(P, H, 128, 2)), np.ascontiguousarray(ometa).view(np.int16))
+    vp = ko.as_f32(v[0].cpu()).reshape(H * P, 128, 128)
+    ovrec, ovmeta = ko.quantize_v_pages(vp)
+    ovrec, ovmeta = ovrec.reshape(H, P, 4096).transpose(1, 0, 2), ovmeta.reshape(H, P, 128, 2).transpose(1, 0, 2, 3)
+    assert np.array_equal(vc.view(P, H, 4096).cpu().numpy(), ovrec)
+    assert np.array_equal(_f16_bits(vm.view(P, H, 128, 2)), np.ascontiguousarray(ovmeta).view(np.int16))

@@ -136,3 +136,43 @@ def test_eager_decode_with_one_call_per_layer_equals_three_calls():
         assert la.PageCount_K == 3            # the flush at step 8 went through both paths
         for n in BUFFERS:
             assert torch.equal(getattr(la, n), getattr(lb, n)), n
+
+
+def test_patched_prefill_honours_the_padding_mask_on_cpu():
+    """A left-padded batch: the stock model masks the padding; the patched forward must hand the same mask to its
+    prompt attention (it used to run plain causal attention and silently attend to the padding)."""
+    from kitty_b200.hf_adapter import patch_model
+
+    cfg, m = _tiny()
+    _, stock = _tiny()
+    stock.load_state_dict(m.state_dict())
+    patch_model(m)
+    ids = torch.randint(0, 1000, (2, 24))
+    mask = torch.ones(2, 24, dtype=torch.long)
+    mask[1, :7] = 0                                            # sequence 1 starts with 7 padding tokens
+    pos = (mask.cumsum(-1) - 1).clamp(min=0)
+    with torch.no_grad():
+        a = m.model(input_ids=ids, attention_mask=mask, position_ids=pos, past_key_values=_PrefillOnlyCache(),
+                    use_cache=True).last_hidden_state
+        b = stock.model(input_ids=ids, attention_mask=mask, position_ids=pos).last_hidden_state
+        c = m.model(input_ids=ids, position_ids=pos, past_key_values=_PrefillOnlyCache(), use_cache=True).last_hidden_state
+    real = mask.bool()
+    assert torch.allclose(a[real], b[real], atol=1e-5)
+    assert not torch.allclose(c[1, 7:], b[1, 7:], atol=1e-3)   # without the mask the padded row differs: the test bites
+
+
+def test_patched_forward_accepts_the_singular_cache_keyword_and_rejects_sliding_windows():
+    from kitty_b200.hf_adapter import patch_model
+
+    cfg, m = _tiny()
+    patch_model(m)
+    attn = m.model.layers[0].self_attn
+    hs = torch.randn(1, 5, 512)
+    pos = m.model.rotary_emb(hs, torch.arange(5).unsqueeze(0))
+    c = _PrefillOnlyCache()
+    with torch.no_grad():
+        out, _ = attn(hs, position_embeddings=pos, past_key_value=c)
+    assert out.shape == (1, 5, 512) and c.quantized == [0]
+    attn.sliding_window = 4096
+    with pytest.raises(NotImplementedError):
+        attn(hs, position_embeddings=pos, past_key_value=c)

@@ -22,6 +22,7 @@ class FakeLayer:
         for c in COUNTERS:
             setattr(self, c, 0)
         self.key_states = self.value_states = None
+        self._ws_box = [None]
         for n in ("PageTable_K", "PageTable_V", "KeyCache", "KeyCache_metadata", "ValueCache", "ValueCache_metadata",
                   "Q_Buffer_K", "Q_Buffer_V"):
             setattr(self, n, None)

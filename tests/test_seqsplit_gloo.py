@@ -103,3 +103,58 @@ def test_two_rank_sequence_split_matches_single_rank():
         assert p.exitcode == 0
     assert sorted(r for r, _ in res) == [0, 1]
     assert all(e < 1e-5 for _, e in res), res
+
+
+def _withhold_worker(rank, world, port, q_out, release):
+    """Rank 1 computes its partial and then never joins the all-gather (it waits on the host until rank 0 has
+    reported): rank 0's collective must end with the process group's timeout and surface as KITTY_E_TIMEOUT."""
+    import datetime
+
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    from kitty_b200 import _lib
+    from kitty_b200.seqsplit import seq_split_decode
+
+    h_kv, h_q, B, L = 1, 4, 1, 32 + 3 * 128 + 9
+    k, v = make_kv(B, h_kv, L, 128, 6, torch.float16)
+    oc = ko.OracleKittyCache(1, h_kv, 128, B, L + 8)
+    oc.update(k, v, 0)
+    oc.quantize_prefill(0)
+    q = torch.randn(B, h_q, 1, 128, generator=torch.Generator().manual_seed(2)).half()
+    lay = oc.kv_cache[0]
+    if rank == 1:
+        release.wait(120)          # withholds its contribution; leaves only after rank 0 has seen the failure
+        q_out.put((rank, "withheld"))
+        return
+    try:
+        seq_split_decode(q, lay, h_kv, 128 ** -0.5, rank=rank, world=world, n_common_pages=lay.PageCount_V,
+                         partial_fn=_oracle_partial(lay, h_kv, h_q), merge_fn=_host_merge)
+        q_out.put((rank, "no error"))
+    except _lib.KittyError as e:
+        q_out.put((rank, e.status))
+    finally:
+        release.set()
+
+
+@pytest.mark.timeout(300)
+def test_withheld_partial_is_reported_as_timeout():
+    from kitty_b200 import _lib
+
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q, release = ctx.Queue(), ctx.Event()
+    procs = [ctx.Process(target=_withhold_worker, args=(r, 2, port, q, release)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=240) for _ in procs)
+    for p in procs:
+        p.join(60)
+        if p.is_alive():
+            p.kill()
+    assert res[1] == "withheld"
+    assert res[0] == _lib.KITTY_E_TIMEOUT, res
