@@ -8,14 +8,19 @@ GPU holds `--batch` sequences).  One step = one decode step of that layer
 through the cache object: append the new token's K/V, fused dequant decode
 attention, flush a full Q-buffer if there is one.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference] [--sweep]
-    python bench.py --workload quantize            # bulk prefill quantize/pack throughput
-    python bench.py --workload e2e [--no-graph]    # Llama-3-8B-shaped decoder, greedy decode with the cache
-    python bench.py --workload seqsplit [--exchange peer] [--seq-batch B]   # 131072-token sequence split over the ranks
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference] [--no-extras]
+    python bench.py --workload quantize            # bulk prefill quantize/pack throughput alone
+    python bench.py --workload e2e [--no-graph]    # Llama-3-8B-shaped decoder, greedy decode with the cache, alone
+    python bench.py --workload seqsplit [--exchange peer] [--seq-batch B]   # 131072-token sequence split over the ranks, alone
 
 Prints one JSON line (rank 0).  `value` is device-timed with the step inputs
 already in HBM; `e2e` runs the same step through the public API from pinned
-host tensors with the result copied back every step.
+host tensors with the result copied back every step (median of 5 repeats of the
+K steps).  The same line carries one short record for each of the other
+workloads, each with its own CUDA-event timing and byte count: `sweep`
+(attention call at batch 1 / 8 / 32), `quantize` (bulk prefill quantize/pack),
+`model_e2e` (decoder model, greedy decode) on one GPU, and `seqsplit` (the
+131072-token sequence split over the ranks) when launched on more than one.
 """
 from __future__ import annotations
 
@@ -34,8 +39,9 @@ sys.path.insert(0, ROOT)
 
 H_KV, H_Q, D, CTX = 8, 32, 128, 32768
 K_PAGE_BYTES, V_PAGE_BYTES = 5760, 4608     # packed record + fp16 metadata per (page, kv-head)
-# dram__bytes_read.sum + dram__bytes_write.sum of decode_paged_i8_kernel divided by the page pairs of the launch,
-# from the ncu capture summarised in profiles/decode_paged_i8_b8_32k_ncu.md (182.71 MB less the 6.66 MB of the 64 edges = 176.05 MB / 16256 pairs)
+# dram__bytes_read.sum + dram__bytes_write.sum of decode_paged_i8_kernel per page pair, from one ncu capture of the
+# batch-8 case of this workload (182.71 MB for the launch less the 6.66 MB of its 64 edges = 176.05 MB over 16256
+# pairs).  A figure from a past capture: it has to be re-taken whenever the streaming kernel's data path changes.
 DRAM_BYTES_PER_PAGE_PAIR = 10829
 
 
@@ -48,7 +54,8 @@ def parse():
     ap.add_argument("--ctx", type=int, default=CTX)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--sweep", action="store_true", help="also time batch 1/8/32 (attention call only)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="only the headline decode workload: skip the sweep / quantize / model_e2e / seqsplit records")
     ap.add_argument("--workload", default="decode", choices=["decode", "quantize", "e2e", "seqsplit"],
                     help="decode (the headline metric), quantize (bulk prefill quantize/pack throughput) or e2e "
                          "(Llama-3-8B-shaped random-init decoder: batch 16, 4096-token prompts, 256 greedy steps)")
@@ -97,8 +104,9 @@ def attention_bytes(lay) -> int:
 # clocks during the timed region (read-only NVML queries)
 # --------------------------------------------------------------------------- #
 class ClockSampler:
-    def __init__(self, index: int):
+    def __init__(self, index: int, interval_s: float = 0.001):
         self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.interval_s = interval_s
         self._stop = threading.Event()
         self._t = None
         try:
@@ -125,7 +133,7 @@ class ClockSampler:
                         self.reasons.add(n)
             except Exception:
                 pass
-            self._stop.wait(0.001)
+            self._stop.wait(self.interval_s)
 
     def __enter__(self):
         if self.nv is not None:
@@ -218,15 +226,21 @@ def build_cache(kb, batch, ctx, extra, device, seed):
     return cache
 
 
-def quantize_workload(args):
+def hbm_peak():
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        return json.load(open(peaks_path))["hbm_gbs"], "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback"
+
+
+def quantize_record(device, steps: int = 3, warmup: int = 3, layers: int = 32) -> dict:
     """Bulk prefill quantize/pack: 65536 tokens x 8 KV heads x head_dim 128 per layer call, bf16 Gaussian K/V with
-    per-(head, channel) scales log-uniform in [1, 16]; 32 layer calls per step (distinct inputs cycle through 4
-    buffers of 268 MB, larger than L2)."""
+    per-(head, channel) scales log-uniform in [1, 16]; `layers` layer calls per step (distinct inputs cycle through 4
+    buffers of 134 MB each for K and for V, larger than L2).  K calls, V calls and the mixed K+V sequence are each
+    timed with CUDA events."""
     import kitty_b200 as kb
 
-    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
-    torch.cuda.set_device(device)
-    T, layers, nbuf = 65536, 32, 4
+    T, nbuf = 65536, 4
     g = torch.Generator(device=device).manual_seed(5)
     ks, vs = [], []
     for _ in range(nbuf):
@@ -241,54 +255,61 @@ def quantize_workload(args):
     vm = torch.zeros(pages, H_KV, 128, 2, dtype=torch.float16, **z)
     pt = torch.arange(pages, dtype=torch.int64, **z).view(1, pages)
 
-    def step():
+    def run(do_k, do_v):
         for l in range(layers):
-            kb.quantize_pack_k(ks[l % nbuf], 0, pages, pt, 0, kc, km, 128, 32)
-            kb.quantize_pack_v(vs[l % nbuf], 0, pages, pt, 0, vc, vm, 128)
+            if do_k:
+                kb.quantize_pack_k(ks[l % nbuf], 0, pages, pt, 0, kc, km, 128, 32)
+            if do_v:
+                kb.quantize_pack_v(vs[l % nbuf], 0, pages, pt, 0, vc, vm, 128)
 
-    W, K = max(3, args.warmup), args.steps
-    for _ in range(W):
-        step()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ek = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
-    e0.record()
-    for i in range(K):
-        step()
-        ek[i][0].record()
-        kb.quantize_pack_k(ks[0], 0, pages, pt, 0, kc, km, 128, 32)       # one extra K call timed alone
-        ek[i][1].record()
-    e1.record()
-    torch.cuda.synchronize()
-    k_ms = sum(a.elapsed_time(b) for a, b in ek) / K
-    ms = (e0.elapsed_time(e1) - k_ms * K) / K
+    def timed(do_k, do_v):
+        for _ in range(warmup):
+            run(do_k, do_v)
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            run(do_k, do_v)
+        e1.record()
+        e1.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    ms_kv, ms_k, ms_v = timed(True, True), timed(True, False), timed(False, True)
     units = layers * pages * H_KV
-    alg = units * (38528 + 37376)
-    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    peak = json.load(open(peaks_path))["hbm_gbs"] if os.path.exists(peaks_path) else 6650.0
-    k_gbs = pages * H_KV * 38528 / (k_ms * 1e-3) / 1e9
-    print(json.dumps({"metric": "prefill_quantize_pack_throughput", "value": alg / (ms * 1e-3) / 1e9, "unit": "GB/s",
-                      "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms, "higher_is_better": True,
-                      "dtype": "f32", "data": "synthetic",
-                      "config": {"workload": "65536 tokens x 32 layers x 8 KV heads x head_dim 128, bf16, K and V"},
-                      "roofline": {"bound": "hbm", "achieved": alg / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
-                                   "frac": alg / (ms * 1e-3) / 1e9 / peak, "traffic": None,
-                                   "pack_k_kernel_GBps": k_gbs, "pack_k_kernel_frac": k_gbs / peak}}))
+    peak, peak_src = hbm_peak()
+    gbs = lambda b, ms: b / (ms * 1e-3) / 1e9
+    kv, k, v = gbs(units * (38528 + 37376), ms_kv), gbs(units * 38528, ms_k), gbs(units * 37376, ms_v)
+    return {"metric": "prefill_quantize_pack_throughput", "value": kv, "unit": "GB/s", "ms_per_step": ms_kv,
+            "steps": steps, "warmup": warmup, "gpu_launches": 2 * layers * steps,
+            "workload": f"65536 tokens x {layers} layer calls x 8 KV heads x head_dim 128, bf16, K and V; in-kernel channel "
+                        "selection; algorithmic bytes 38528 (K) / 37376 (V) per page-head",
+            "roofline": {"bound": "hbm", "achieved": kv, "peak": peak, "unit": "GB/s", "frac": kv / peak, "traffic": None,
+                         "peak_source": peak_src,
+                         "pack_k_kernel": {"GBps": k, "frac": k / peak, "ms_per_layer_call": ms_k / layers},
+                         "pack_v_kernel": {"GBps": v, "frac": v / peak, "ms_per_layer_call": ms_v / layers}}}
 
 
-def e2e_workload(args):
+def quantize_workload(args):
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    r = quantize_record(device, steps=args.steps, warmup=max(3, args.warmup))
+    r.update({"n_gpus": 1, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+              "config": {"workload": r.pop("workload")}})
+    print(json.dumps(r))
+
+
+def model_record(device, layers: int = 32, B: int = 16, steps: int = 256, graph: bool = True, runs: int = 1) -> dict:
     """Random-init Llama-3-8B-shaped decoder (hidden 4096, 32q/8kv heads, head_dim 128, inter 14336, vocab 128256),
     bf16, batch 16, prompts of 4096 uniform-random token ids (seed 0), 256 greedy decode steps with a fresh
-    KittyCache — the method of the reference's latency benchmark (fresh cache, greedy, fixed length)."""
+    KittyCache per run — the method of the reference's latency benchmark (fresh cache, greedy, fixed length;
+    latency_benchmarking/benchmark_kitty.py:154-183)."""
     from transformers import LlamaConfig, LlamaForCausalLM
 
     import kitty_b200 as kb
     from kitty_b200.hf_adapter import GraphedDecoder, patch_model
 
-    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
-    torch.cuda.set_device(device)
-    B, L, steps = args.e2e_batch, 4096, args.e2e_steps
-    cfg = LlamaConfig(hidden_size=4096, intermediate_size=14336, num_hidden_layers=args.layers, num_attention_heads=32,
+    L = 4096
+    cfg = LlamaConfig(hidden_size=4096, intermediate_size=14336, num_hidden_layers=layers, num_attention_heads=32,
                       num_key_value_heads=8, head_dim=128, vocab_size=128256, max_position_embeddings=8192,
                       rope_theta=500000.0, tie_word_embeddings=False)
     torch.manual_seed(0)
@@ -300,6 +321,7 @@ def e2e_workload(args):
     patch_model(model)
     g = torch.Generator().manual_seed(0)
     ids = torch.randint(0, 128256, (B, L), generator=g).to(device)
+    steady = []
 
     def run():
         cache = kb.get_kvcache_kitty(cfg, B, L + steps + 8, device=device)
@@ -311,7 +333,8 @@ def e2e_workload(args):
             tok = model.lm_head(hs[:, -1:, :]).argmax(-1)
             torch.cuda.synchronize()
             t1 = time.perf_counter()
-            if args.graph:
+            th = t1
+            if graph:
                 dec = GraphedDecoder(model, cache, B)
                 dec.tok.copy_(tok)
                 dec.pos.fill_(L)
@@ -334,27 +357,147 @@ def e2e_workload(args):
         steady.append((t2 - th) / (steps - steps // 2) * 1e3)
         return t1 - t0, t2 - t1
 
-    steady = []
-
     run()                                   # warm-up generate (fresh cache per run, as the reference benchmark does)
-    pre, dec = zip(*[run() for _ in range(max(1, min(args.steps, 3)))])
+    pre, dec = zip(*[run() for _ in range(max(1, runs))])
     dec_s, pre_s = min(dec), min(pre)
-    print(json.dumps({"metric": "e2e_decode_tokens_per_s", "value": B * (steps - 1) / dec_s, "unit": "tokens/s",
-                      "n_gpus": 1, "steps": steps, "ms_per_step": dec_s / (steps - 1) * 1e3, "higher_is_better": True,
-                      "dtype": "bf16", "data": "synthetic",
-                      "config": {"workload": f"random-init Llama-3-8B shape, {args.layers} layers, batch {B}, prompt 4096, "
-                                             f"{steps} greedy steps, KittyCache" + (", decode steps replayed from one CUDA graph (capture included)"
-                                                                              if args.graph else ""), "prefill_s": pre_s, "decode_s": dec_s, "steady_ms_per_step": min(steady[1:]),
-                                 "generate_s": pre_s + dec_s}}))
+    del model
+    torch.cuda.empty_cache()
+    return {"metric": "e2e_decode_tokens_per_s", "value": B * (steps - 1) / dec_s, "unit": "tokens/s",
+            "ms_per_step": dec_s / (steps - 1) * 1e3, "steady_ms_per_step": min(steady[1:]), "steps": steps,
+            "prefill_s": pre_s, "decode_s": dec_s, "generate_s": pre_s + dec_s, "dtype": "bf16", "timing": "host clock "
+            "around the whole greedy decode, device synchronised on both sides",
+            "workload": f"random-init Llama-3-8B shape, {layers} layers, batch {B}, prompt 4096, {steps} greedy steps, "
+                        "KittyCache" + (", decode steps replayed from one CUDA graph (capture included)" if graph else "")}
+
+
+def e2e_workload(args):
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    r = model_record(device, args.layers, args.e2e_batch, args.e2e_steps, args.graph, runs=max(1, min(args.steps, 3)))
+    r.update({"n_gpus": 1, "higher_is_better": True, "data": "synthetic", "config": {"workload": r.pop("workload")}})
+    print(json.dumps(r))
+
+
+def sweep_record(kb, device, ctx: int, batches=(1, 8, 32)) -> dict:
+    """The attention call alone (kitty_attention_forward) at small batches, L2 flushed before every call."""
+    mod = argparse.Namespace(num_attention_heads=H_Q, num_key_value_heads=H_KV)
+    peak, _ = hbm_peak()
+    sweep = {}
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    for b in batches:
+        c2 = build_cache(kb, b, ctx, 64, device, seed=7)
+        l2 = c2.kv_cache[0]
+        q = torch.randn(b, H_Q, 1, D, device=device).to(torch.bfloat16)
+        c2.update(torch.randn(b, H_KV, 1, D, device=device).to(torch.bfloat16),
+                  torch.randn(b, H_KV, 1, D, device=device).to(torch.bfloat16), 0)
+        for _ in range(5):
+            kb.kitty_attention_forward(mod, q, l2, D ** -0.5)
+        a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        times = []
+        for _ in range(30):
+            flush_buf.zero_()                      # evict the cache from L2 between iterations
+            a.record()
+            kb.kitty_attention_forward(mod, q, l2, D ** -0.5)
+            z.record()
+            z.synchronize()
+            times.append(a.elapsed_time(z))
+        us = statistics.median(times) * 1e3
+        alg = b * attention_bytes(l2)
+        sweep[f"batch{b}"] = {"us_per_call": us, "algorithmic_bytes": alg, "GBps": alg / (us * 1e-6) / 1e9,
+                              "frac_of_peak": alg / (us * 1e-6) / 1e9 / peak}
+        del c2
+    sweep["how"] = "median of 30 calls, CUDA events around the call, a 256 MB buffer written before each (L2 flushed)"
+    return sweep
+
+
+def seqsplit_measure(kb, device, rank, world, dist, steps, warmup, seq_batch, exchange, tail_weight):
+    """Per-layer-step latency (us, max over ranks) of the long-context shape: 28 query / 4 KV heads, 131072 cached
+    tokens, the common pages split in contiguous ranges over `world` ranks (sink on rank 0, tail on the last rank).
+    NL layers' caches take turns so that every step reads cold pages (NL x 43 MB per sequence > L2) and the steps
+    are queued back to back, as the layers of a model are; the same seeds on every rank: same sequences."""
+    global H_KV, H_Q
+    from kitty_b200.seqsplit import PartialExchange, seq_split_decode
+
+    saved = (H_KV, H_Q)
+    H_KV, H_Q = 4, 28
+    try:
+        ctx = 131072
+        W, K, SB = max(3, warmup), steps, seq_batch
+        NL = 8 if SB * 8 * 43 <= 4000 else 4
+        caches = [build_cache(kb, SB, ctx, (W + K) // NL + 2, device, seed=4321 + j) for j in range(NL)]
+        lay = caches[0].kv_cache[0]
+        g = torch.Generator(device=device).manual_seed(17)
+        qs = torch.randn(W + K, SB, H_Q, 1, D, generator=g, device=device).to(torch.bfloat16)
+        ks = torch.randn(W + K, SB, H_KV, 1, D, generator=g, device=device).to(torch.bfloat16)
+        vs = torch.randn(W + K, SB, H_KV, 1, D, generator=g, device=device).to(torch.bfloat16)
+        xch = PartialExchange(SB * H_Q, device) if (exchange == "peer" and world > 1) else None
+
+        def step(i):
+            cache = caches[i % NL]
+            layer = cache.kv_cache[0]
+            cache.update(ks[i], vs[i], 0)
+            out = seq_split_decode(qs[i], layer, H_KV, D ** -0.5, rank=rank, world=world,
+                                   n_common_pages=layer.PageCount_V, exchange=xch, tail_weight=tail_weight)
+            cache.quantize_decode(0)
+            return out
+
+        for i in range(W):
+            step(i)
+        torch.cuda.synchronize(device)
+        if dist is not None and world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(K):
+            step(W + i)
+        e1.record()
+        e1.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], device=device, dtype=torch.float64)
+        if dist is not None and world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if xch is not None:
+            xch.check()
+        packed = SB * H_KV * (lay.PageCount_K * K_PAGE_BYTES + lay.PageCount_V * V_PAGE_BYTES)
+        return float(t[0]) / K * 1e3, packed, NL
+    finally:
+        H_KV, H_Q = saved
+
+
+def seqsplit_record(kb, device, rank, world, dist, steps: int = 48, warmup: int = 8) -> dict:
+    """The long-context configuration on `world` GPUs: per-layer-step latency with the two ways of combining the
+    partials, next to the same sequence reduced by one GPU alone (rank 0's figure; the other ranks wait)."""
+    rec = {"workload": "1 layer step, 28q/4kv heads, 131072 cached tokens, sequence split over the ranks in contiguous "
+                       "page ranges; 8 layers' caches in turn (cold pages every step), steps queued back to back; CUDA "
+                       "events, max over ranks", "n_gpus": world, "steps": steps, "unit": "us"}
+    peak, _ = hbm_peak()
+    for sb in (1, 8):
+        one = torch.zeros(1, device=device, dtype=torch.float64)
+        if rank == 0:
+            us1, packed, _ = seqsplit_measure(kb, device, 0, 1, None, steps, warmup, sb, "nccl", 0)
+            one[0] = us1
+        if world > 1:
+            dist.all_reduce(one, op=dist.ReduceOp.MAX)
+        us1 = float(one[0])
+        r = {"one_gpu_us": us1}
+        for ex in ("peer", "nccl"):
+            us, packed, _ = seqsplit_measure(kb, device, rank, world, dist, steps, warmup, sb, ex, 0)
+            r[f"{ex}_us"] = us
+            r[f"{ex}_speedup_vs_one_gpu"] = us1 / us
+            r[f"{ex}_strong_scaling_efficiency"] = us1 / us / world
+            r[f"{ex}_packed_kv_GBps_aggregate"] = packed / (us * 1e-6) / 1e9
+        r["packed_kv_bytes"] = packed
+        r["one_gpu_frac_of_peak"] = packed / (us1 * 1e-6) / 1e9 / peak
+        rec[f"batch{sb}"] = r
+    rec["collective"] = {"peer": "none: the attention call's merge step stores the partials into every rank's buffer over "
+                                 "NVLink and waits (bounded) for the others (kitty_decode_attn_exchange)",
+                         "nccl": "all_gather of [28,130] fp32 per rank + kitty_lse_merge"}
+    return rec
 
 
 def seqsplit_workload(args):
-    """Long-context layer step: 28 query / 4 KV heads, batch 1, 131072 cached tokens, the 1022 common pages split in
-    contiguous ranges over the ranks (sink on rank 0, tail on the last rank); per step every rank reduces its range,
-    the [28, 130] fp32 partials are all-gathered over NCCL and merged.  Launch under torchrun for N > 1."""
-    global H_KV, H_Q
+    """The sequence-split workload alone.  Launch under torchrun for N > 1."""
     import kitty_b200 as kb
-    from kitty_b200.seqsplit import PartialExchange, seq_split_decode
 
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
@@ -364,63 +507,28 @@ def seqsplit_workload(args):
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=device)
-    H_KV, H_Q = 4, 28
-    ctx = 131072
-    W, K = max(3, args.warmup), args.steps
-    SB = args.seq_batch
-    # NL layers' caches take turns so that every step reads cold pages (NL x 43 MB per sequence > L2) and the steps
-    # can be queued back to back, as the layers of a model are; the same seeds on every rank: same sequences.
-    NL = 8 if SB * 8 * 43 <= 4000 else 4
-    caches = [build_cache(kb, SB, ctx, (W + K) // NL + 2, device, seed=4321 + j) for j in range(NL)]
-    lay = caches[0].kv_cache[0]
-    g = torch.Generator(device=device).manual_seed(17)
-    qs = torch.randn(W + K, SB, H_Q, 1, D, generator=g, device=device).to(torch.bfloat16)
-    ks = torch.randn(W + K, SB, H_KV, 1, D, generator=g, device=device).to(torch.bfloat16)
-    vs = torch.randn(W + K, SB, H_KV, 1, D, generator=g, device=device).to(torch.bfloat16)
-
-    xch = PartialExchange(SB * H_Q, device) if (args.exchange == "peer" and world > 1) else None
-
-    def step(i):
-        cache = caches[i % NL]
-        layer = cache.kv_cache[0]
-        cache.update(ks[i], vs[i], 0)
-        out = seq_split_decode(qs[i], layer, H_KV, D ** -0.5, rank=rank, world=world,
-                               n_common_pages=layer.PageCount_V, exchange=xch, tail_weight=args.tail_weight)
-        cache.quantize_decode(0)
-        return out
-
-    for i in range(W):
-        step(i)
-    torch.cuda.synchronize(device)
-    if dist is not None:
-        dist.barrier()
-    torch.cuda.synchronize(device)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(K):
-        step(W + i)
-    e1.record()
-    e1.synchronize()
-    tot = e0.elapsed_time(e1)
-    t = torch.tensor([tot], device=device, dtype=torch.float64)
-    if dist is not None:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t[0]) / K
-    if xch is not None:
-        xch.check()
+    us, packed, NL = seqsplit_measure(kb, device, rank, world, dist, args.steps, args.warmup, args.seq_batch,
+                                      args.exchange, args.tail_weight)
     if rank == 0:
-        packed = SB * H_KV * (lay.PageCount_K * K_PAGE_BYTES + lay.PageCount_V * V_PAGE_BYTES)
-        print(json.dumps({"metric": "seqsplit_layer_step_latency", "value": ms * 1e3, "unit": "us", "n_gpus": world,
-                          "steps": K, "warmup": W, "higher_is_better": False, "dtype": "f16", "data": "synthetic",
-                          "packed_kv_GBps_aggregate": packed / (ms * 1e-3) / 1e9,
-                          "config": {"workload": f"1 layer, 28q/4kv heads, batch {SB}, 131072 cached tokens, sequence split "
-                                                 f"over {world} GPU(s) (tail weight {args.tail_weight}), {NL} layers' caches in turn (cold pages every step), steps queued "
-                                                 "back to back",
-                                     "collective": ("none: partials stored into every rank's buffer over NVLink by the merge "
-                                                    "kernel of the attention call (kitty_decode_attn_exchange)") if xch is not None else
-                                     "all_gather of [28,130] fp32 per rank + merge"}}))
+        print(json.dumps({"metric": "seqsplit_layer_step_latency", "value": us, "unit": "us", "n_gpus": world,
+                          "steps": args.steps, "warmup": max(3, args.warmup), "higher_is_better": False, "dtype": "f16",
+                          "data": "synthetic", "packed_kv_GBps_aggregate": packed / (us * 1e-6) / 1e9,
+                          "config": {"workload": f"1 layer, 28q/4kv heads, batch {args.seq_batch}, 131072 cached tokens, "
+                                                 f"sequence split over {world} GPU(s) (tail weight {args.tail_weight}), "
+                                                 f"{NL} layers' caches in turn (cold pages every step), steps queued back to back",
+                                     "collective": "peer-memory exchange inside the attention call" if args.exchange == "peer"
+                                     and world > 1 else "all_gather of [28,130] fp32 per rank + merge"}}))
     if dist is not None:
         dist.destroy_process_group()
+
+
+def decode_config(ctx: int, B: int, world: int) -> dict:
+    """The `config` of the headline line, identical in both arms (the reference arm times a bounded sample of it)."""
+    p = partition(ctx)
+    return {"workload": f"decode step, 1 layer, 32q/8kv heads, head_dim 128, {ctx} cached tokens, bf16 q/k/v, "
+                        "2-bit K (25% channels 4-bit) / 2-bit V pages",
+            "batch_per_gpu": B, "global_batch": B * world, "parallelism": f"batch-sharded x{world}, no collective",
+            "l2": f"inputs larger than L2 ({B * packed_bytes(p['pages_k'], p['pages_v']) / 1e6:.0f} MB of packed pages per GPU per step)"}
 
 
 def main():
@@ -442,8 +550,9 @@ def main():
         line = {"impl": "reference", "metric": "decode_attn_packed_kv_throughput", "value": r["value"], "unit": "GB/s",
                 "n_gpus": args.gpus, "steps": r["steps"], "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": f"decode step, 1 layer, 32q/8kv heads, head_dim 128, {args.ctx} cached tokens",
-                           "batch_per_gpu": 1, "l2": "inputs larger than L2"},
+                "config": decode_config(args.ctx, args.batch, args.gpus),
+                "sample_note": "each step is ONE sequence of the configuration's batch (the reference's PyTorch path in "
+                               "fp32 on the host cores); throughput is per byte of packed KV, so the sample scales",
                 "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
                 "decode_tokens_per_s": r["tokens_per_s"],
                 "e2e": {"value": r["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -467,16 +576,19 @@ def main():
     B, W, K = args.batch, args.warmup, args.steps
     if W < 3:
         W = 3
-    total = 2 * (W + K)                         # device-timed pass, then the end-to-end pass
+    E2E_REPEATS = 5
+    total = (W + K) + (W + E2E_REPEATS * K)     # device-timed pass, then the end-to-end pass
     cache = build_cache(kb, B, args.ctx, total, device, seed=1234 + rank)
     lay = cache.kv_cache[0]
     mod = argparse.Namespace(num_attention_heads=H_Q, num_key_value_heads=H_KV)
     scaling = D ** -0.5
     g = torch.Generator(device=device).manual_seed(99 + rank)
-    qs = torch.randn(total, B, H_Q, 1, D, generator=g, device=device).to(torch.bfloat16)
-    ks = torch.randn(total, B, H_KV, 1, D, generator=g, device=device).to(torch.bfloat16)
-    vs = torch.randn(total, B, H_KV, 1, D, generator=g, device=device).to(torch.bfloat16)
+    n_dev = W + K
+    qs = torch.randn(n_dev, B, H_Q, 1, D, generator=g, device=device).to(torch.bfloat16)
+    ks = torch.randn(n_dev, B, H_KV, 1, D, generator=g, device=device).to(torch.bfloat16)
+    vs = torch.randn(n_dev, B, H_KV, 1, D, generator=g, device=device).to(torch.bfloat16)
     launches = {"n": 0}
+    flush_log = []
 
     def step(q, k, v):
         cache.update(k, v, 0)
@@ -484,6 +596,7 @@ def main():
         flush = lay.Q_Buffer_Count_K == 128 or lay.Q_Buffer_Count_V == 128
         cache.quantize_decode(0)
         launches["n"] += 3 + (1 if flush else 0)      # append, streaming (pages + edges), merge (+ flush)
+        flush_log.append(flush)
         return out
 
     def barrier():
@@ -497,6 +610,7 @@ def main():
         step(qs[i], ks[i], vs[i])
     barrier()
     launches["n"] = 0
+    flush_log.clear()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     attn_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
     packed = attn_alg = 0
@@ -513,22 +627,29 @@ def main():
             flush = lay.Q_Buffer_Count_K == 128 or lay.Q_Buffer_Count_V == 128
             cache.quantize_decode(0)
             launches["n"] += 3 + (1 if flush else 0)
+            flush_log.append(flush)
         ev1.record()
         barrier()
     ms = ev0.elapsed_time(ev1)
     attn_ms = sum(a.elapsed_time(b) for a, b in attn_ev)
     gpu_launches = launches["n"]
+    flush_steps_value = [i for i, f in enumerate(flush_log) if f]
     t = torch.tensor([ms, attn_ms], device=device, dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, attn_ms = float(t[0]), float(t[1])
     value = world * packed / (ms * 1e-3) / 1e9
     tokens_per_s = world * B * K / (ms * 1e-3)
+    del qs, ks, vs
 
     # ---------------- end-to-end pass: pinned host inputs, result copied back every step ---------------- #
-    # one pinned buffer per step, [q | k | v] back to back: a single host-to-device copy
+    # one pinned buffer per step, [q | k | v] back to back: a single host-to-device copy.  E2E_REPEATS repeats of the
+    # K steps are timed one by one (host clock, barrier on both sides) and the median repeat is reported: a step here
+    # is bound by host latency (copy in, launch, copy out, synchronise), which is noisy over a few milliseconds.
     nq, nk = B * H_Q * D, B * H_KV * D
-    hin = torch.cat([qs[W + K:].reshape(-1, nq), ks[W + K:].reshape(-1, nk), vs[W + K:].reshape(-1, nk)], dim=1).cpu().pin_memory()
+    n_e2e = W + E2E_REPEATS * K
+    gh = torch.Generator().manual_seed(7 + rank)
+    hin = torch.randn(n_e2e, nq + 2 * nk, generator=gh).to(torch.bfloat16).pin_memory()
     hout = torch.empty(B, 1, H_Q, D, dtype=torch.bfloat16).pin_memory()
 
     def e2e_step(i):
@@ -543,53 +664,74 @@ def main():
     for i in range(W):
         e2e_step(i)
     barrier()
-    packed_e = 0
-    with ClockSampler(local_rank) as clocks_e:      # second timed region: its samples join the first region's
-        t0 = time.perf_counter()
-        for i in range(K):
-            e2e_step(W + i)
-            packed_e += B * packed_bytes(lay.PageCount_K, lay.PageCount_V)
-        barrier()
-        e2e_s = time.perf_counter() - t0
+    flush_log.clear()
+    rep_s, rep_bytes = [], []
+    with ClockSampler(local_rank, interval_s=0.005) as clocks_e:      # second timed region: its samples join the first region's
+        for r in range(E2E_REPEATS):
+            nbytes = 0
+            t0 = time.perf_counter()
+            for i in range(K):
+                e2e_step(W + r * K + i)
+                nbytes += B * packed_bytes(lay.PageCount_K, lay.PageCount_V)
+            barrier()
+            rep_s.append(time.perf_counter() - t0)
+            rep_bytes.append(nbytes)
     clocks.samples += clocks_e.samples
     clocks.reasons |= clocks_e.reasons
-    te = torch.tensor([e2e_s], device=device, dtype=torch.float64)
+    te = torch.tensor(rep_s, device=device, dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    e2e_s = float(te[0])
+    rep_s = [float(x) for x in te]
+    mid = sorted(range(E2E_REPEATS), key=lambda r: rep_s[r])[E2E_REPEATS // 2]
+    e2e_s, packed_e = rep_s[mid], rep_bytes[mid]
+    flush_steps_e2e = [i for i, f in enumerate(flush_log) if f]
     h2d = B * (H_Q + 2 * H_KV) * D * 2
     d2h = B * H_Q * D * 2
     from kitty_b200.attention import workspace_status
 
     if workspace_status(lay) != 0:
         raise SystemExit("device-side bounded wait ran out during the benchmark")
+    pages_v = lay.PageCount_V
+    del cache, lay, hin
+    torch.cuda.empty_cache()
+
+    # ---------------- records of the other workloads (own timing each) ---------------- #
+    extras = {}
+    if not args.no_extras:
+        if world == 1:
+            extras["sweep"] = sweep_record(kb, device, args.ctx)
+            extras["quantize"] = quantize_record(device)
+            torch.cuda.empty_cache()
+            extras["model_e2e"] = model_record(device)
+        else:
+            extras["seqsplit"] = seqsplit_record(kb, device, rank, world, dist)
 
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return
 
-    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(peaks_path):
-        peak, peak_src = json.load(open(peaks_path))["hbm_gbs"], "measured (MEASURED_PEAKS.json hbm_gbs)"
-    else:
-        peak, peak_src = 6650.0, "fallback"
+    peak, peak_src = hbm_peak()
     achieved = (attn_alg / K) / (attn_ms / K * 1e-3) / 1e9     # per attention call, this rank
     line = {
         "metric": "decode_attn_packed_kv_throughput", "value": value, "unit": "GB/s", "n_gpus": world, "steps": K,
         "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic",
-        "config": {"workload": f"decode step, 1 layer, 32q/8kv heads, head_dim 128, {args.ctx} cached tokens, bf16 q/k/v, "
-                               "2-bit K (25% channels 4-bit) / 2-bit V pages",
-                   "batch_per_gpu": B, "global_batch": B * world, "parallelism": f"batch-sharded x{world}, no collective",
-                   "l2": f"inputs larger than L2 ({B * packed_bytes(lay.PageCount_K, lay.PageCount_V) / 1e6:.0f} MB of packed pages per GPU per step)"},
+        "dtype_note": "arithmetic type of the path: q/k/v arrive as bf16, the cache's full-precision buffers and the "
+                      "(scale, min) metadata are fp16 as in the reference, dequantisation and softmax accumulate in fp32",
+        "config": decode_config(args.ctx, B, world),
+        "flush_steps": {"value": flush_steps_value, "e2e": flush_steps_e2e,
+                        "note": "indices of the timed steps in which a full Q-buffer was quantized into a page (the "
+                                "Q-buffers hold 96 tokens after the prompt, so the first flush is the 32nd step after "
+                                "it); e2e: indices over all 5 repeats"},
         "decode_tokens_per_s": tokens_per_s,
         "e2e": {"value": world * packed_e / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s / K * 1e3, "decode_tokens_per_s": world * B * K / e2e_s},
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s / K * 1e3, "decode_tokens_per_s": world * B * K / e2e_s,
+                "repeats": E2E_REPEATS, "repeat_ms_per_step": [x / K * 1e3 for x in rep_s], "statistic": "median repeat"},
         "gpu_launches": gpu_launches,
         "clocks": clocks.summary(),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": B * H_KV * lay.PageCount_V * DRAM_BYTES_PER_PAGE_PAIR, "peak_source": peak_src,
+                     "traffic": B * H_KV * pages_v * DRAM_BYTES_PER_PAGE_PAIR, "peak_source": peak_src,
                      "kernel": "decode attention call = decode_paged_i8_kernel (page pairs and edges, >97 % of the "
                                "step's device time in the ncu launch list) + merge_kernel; achieved = algorithmic bytes of "
                                "the call / CUDA-event time of the call; traffic = ncu DRAM bytes of the streaming "
@@ -599,31 +741,7 @@ def main():
     if world == 1 and not args.no_cpu_baseline:
         r = cpu_reference(args.ctx, 40, 2, budget_s=20.0)
         line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
-    if args.sweep and world == 1:
-        sweep = {}
-        for b in (1, 8, 32):
-            c2 = build_cache(kb, b, args.ctx, 64, device, seed=7)
-            l2 = c2.kv_cache[0]
-            q = torch.randn(b, H_Q, 1, D, device=device).to(torch.bfloat16)
-            c2.update(torch.randn(b, H_KV, 1, D, device=device).to(torch.bfloat16),
-                      torch.randn(b, H_KV, 1, D, device=device).to(torch.bfloat16), 0)
-            for _ in range(5):
-                kb.kitty_attention_forward(mod, q, l2, scaling)
-            a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=device)
-            tot = 0.0
-            for _ in range(20):
-                flush_buf.zero_()                      # evict the cache from L2 between iterations
-                a.record()
-                kb.kitty_attention_forward(mod, q, l2, scaling)
-                z.record()
-                z.synchronize()
-                tot += a.elapsed_time(z)
-            us = tot / 20 * 1e3
-            sweep[f"batch{b}"] = {"us_per_call": us, "GBps": b * attention_bytes(l2) / (us * 1e-6) / 1e9,
-                                  "frac_of_peak": b * attention_bytes(l2) / (us * 1e-6) / 1e9 / peak}
-            del c2, flush_buf
-        line["sweep_attention_call_l2_flushed"] = sweep
+    line.update(extras)
     print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()

@@ -6,7 +6,8 @@ its accuracy runs (src/kitty_sim): keys are fake-quantized channel-wise per
 and attention is plain eager attention over the dequantized tensors.  That is
 the reference's CPU-runnable path; this file restates it so that the benchmark
 can time it on the GPU box's host cores, where the reference checkout does not
-exist.  It is never imported by the product package.
+exist.  It is never imported by the product package.  Pinned: tests/test_sim_port_golden.py
+compares it bit for bit with outputs of the reference's own simulator (tests/golden/sim_port.npz).
 
 Restated from (paths inside the reference project):
   src/kitty_sim/utils_quant.py:12-114      build_promote_mask, fake_quant_groupwise_lastdim
@@ -69,6 +70,7 @@ class SimKittyCache:
     def update(self, k: torch.Tensor, v: torch.Tensor):
         if self.k is None:                                   # prefill
             self.k, self.v = k.detach().clone(), v.detach().clone()
+            keys, values = self.k.detach().clone(), self.v.detach().clone()   # post-quant: the prompt step sees full precision
             L = self.k.shape[-2]
             if L > self.sink + self.buffer:
                 n = L - self.sink
@@ -77,7 +79,7 @@ class SimKittyCache:
                     self.k[:, :, i:i + self.buffer] = self._quant_k(self.k[:, :, i:i + self.buffer])
                 end = self.sink + n - self.buffer            # values: everything but the newest `buffer` tokens
                 self.v[:, :, self.sink:end] = fake_quant_lastdim(self.v[:, :, self.sink:end], self.group, self.vbits)
-            return self.k, self.v
+            return keys, values
         self.k = torch.cat([self.k, k], dim=-2)
         self.v = torch.cat([self.v, v], dim=-2)
         keys, values = self.k.detach().clone(), self.v.detach().clone()      # post-quant: this step sees full precision

@@ -126,8 +126,7 @@ def test_fused_selection_rates_against_torch_topk(kb, dtype):
     assert torch.equal(a, b) and torch.equal(km[same], km_t[same])
     _record(f"selection_rates_{str(dtype).split('.')[-1]}.json",
             {"page_heads": H * P, "exact_index_bytes": exact, "same_boosted_set": same_set, "valid_top32_set": valid})
-    assert valid >= 0.98, (exact, same_set, valid)
-    assert same_set >= 0.90, (exact, same_set, valid)
+    assert valid >= 0.999 and same_set >= 0.999, (exact, same_set, valid)
 
 
 # --------------------------------------------------------------------------- #
@@ -193,12 +192,16 @@ def test_tiny_llama_logits_follow_the_oracle_cache_through_flushes(kb):
             assert worst <= ATTN_TOL, (s, worst)
             tok = b.argmax(-1, keepdim=True)                  # both sides are fed the host's greedy token
             pos = torch.full((1, 1), L + s, dtype=torch.long)
-    lay, olay = cache.kv_cache[1], ocache.kv_cache[1]
-    assert [getattr(lay, c) for c in COUNTERS] == [getattr(olay, c) for c in COUNTERS]
-    assert lay.PageCount_K == (L + steps - 1 - 32) // 128 and lay.PageCount_K >= 4
-    same = np.mean(lay.KeyCache.cpu().numpy() == olay.KeyCache)
-    assert same > 0.999, same          # fp32 GEMMs on the two machines differ in the last bits: a few codes may flip
-    _record("tiny_llama_logits.json", {"steps": steps, "worst_rel_err": worst, "key_cache_bytes_equal": float(same)})
+    same = []
+    for lay, olay in zip(cache.kv_cache, ocache.kv_cache):
+        assert [getattr(lay, c) for c in COUNTERS] == [getattr(olay, c) for c in COUNTERS]
+        assert lay.PageCount_K == (L + steps - 1 - 32) // 128 and lay.PageCount_K >= 4
+        same.append(float(np.mean(lay.KeyCache.cpu().numpy() == olay.KeyCache)))
+    # Layer 0's keys depend only on the embedding and one projection: fp32 GEMMs of the two machines differ in the last
+    # bits, so at most a handful of codes flip.  Layer 1's input carries layer 0's attention output, which agrees to
+    # the attention tolerance only: more elements sit on the other side of a rounding boundary.
+    assert same[0] > 0.9999 and same[1] > 0.99, same
+    _record("tiny_llama_logits.json", {"steps": steps, "worst_rel_err": worst, "key_cache_bytes_equal": same})
 
 
 # --------------------------------------------------------------------------- #
