@@ -81,6 +81,7 @@ int launch_append_dyn(const kitty_layer &L, const kitty_step_state *dyn, const v
 int launch_flush_dyn(const kitty_layer &L, const kitty_step_state *dyn, int32_t B, int div_mode, cudaStream_t s);
 int launch_merge(const MergeArgs &m, cudaStream_t s);
 int sm_count();        // multiprocessors of the current device (cached per device)
+int i8_blocks_per_sm(int G);   // resident blocks per multiprocessor of the integer streaming kernel for groups of G heads
 
 __device__ __forceinline__ float load_q(const void *q, int dtype, int64_t i) {
   if (dtype == KITTY_F16) return __half2float(static_cast<const __half *>(q)[i]);

@@ -133,9 +133,9 @@ static int decode_attn_core(const kitty_layer *layer, const kitty_counts *counts
   P.n_tiles = 1 + static_cast<int>((tk + PAGE - 1) / PAGE);
   P.has_sink = ((flags & 1) && C.Sink_Count > 0) ? 1 : 0;
   P.has_tail = ((flags & 2) && (P.n_tiles - 1 - pv) > 0) ? 1 : 0;
-  const bool use_i8 = (impl == 0 && G <= 4);       // integer tensor-core kernel: 4 heads x (high, low) limb columns
+  const bool use_i8 = (impl == 0 && G <= 8);       // integer tensor-core kernel: one or two operand groups of 4 heads
   const int n_gt = use_i8 ? 1 : (G + 7) / 8;
-  const int grid_max = (use_i8 ? 4 : 2) * sm_count();        // resident blocks per SM of the streaming kernel
+  const int grid_max = (use_i8 ? i8_blocks_per_sm(G) : 2) * sm_count();   // resident blocks per SM of the streaming kernel
   P.fast_chunks = (impl != 1) ? 1 : 0;
   plan_edge(P.has_sink, P.has_tail, C, static_cast<int64_t>(B) * H, P.fast_chunks != 0, &P.edge_parts, &P.edge_part_tok);
   // static item assignment (fp16 kernel): leave blocks for the edge parts so that a small call is one wave
@@ -322,10 +322,10 @@ extern "C" int kitty_plan_step(const kitty_layer *layer, const kitty_counts *bef
   st.n_tiles = 1 + static_cast<int>((tk + PAGE - 1) / PAGE);
   st.has_sink = c.Sink_Count > 0 ? 1 : 0;
   st.has_tail = (st.n_tiles - 1 - pv) > 0 ? 1 : 0;
-  // the same plan kitty_decode_attn makes for these counters: int8 kernel for groups of up to 4 heads, fp16 kernel above
-  const bool use_i8 = G <= 4;
+  // the same plan kitty_decode_attn makes for these counters: int8 kernel for groups of up to 8 heads, fp16 kernel above
+  const bool use_i8 = G <= 8;
   const int n_gt = use_i8 ? 1 : (G + 7) / 8;
-  const int grid_max = (use_i8 ? 4 : 2) * sm_count();
+  const int grid_max = (use_i8 ? i8_blocks_per_sm(G) : 2) * sm_count();
   plan_edge(st.has_sink, st.has_tail, c, static_cast<int64_t>(B) * H, true, &st.edge_parts, &st.edge_part_tok);
   const int64_t edge_blocks = use_i8 ? 0 : std::min<int64_t>(static_cast<int64_t>(B) * H * st.edge_parts, grid_max / 2);
   plan_chunks(pv, static_cast<int64_t>(B) * H * n_gt, grid_max - static_cast<int>(edge_blocks), use_i8, &st.ch, &st.nchunk);
@@ -382,8 +382,8 @@ extern "C" int kitty_decode_step(const kitty_layer *layer, const kitty_step_stat
   a.partials = reinterpret_cast<float *>(static_cast<uint8_t *>(workspace) + WS_HEADER);
   a.dyn = device_state;
   // fixed grids: the item counts are read on the device
-  if (G <= 4) {
-    if (int rc = launch_decode_paged_i8(a, 0, 0, 4 * sm_count(), s, true)) return rc;
+  if (G <= 8) {
+    if (int rc = launch_decode_paged_i8(a, 0, 0, i8_blocks_per_sm(G) * sm_count(), s, true)) return rc;
   } else {
     if (int rc = launch_decode_paged(a, 0, (G + 7) / 8, 0, 2 * sm_count(), s, true)) return rc;
   }

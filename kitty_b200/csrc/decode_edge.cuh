@@ -31,7 +31,7 @@ constexpr int S_ROW = EDGE_MAX_TOK + 4;
 // RB_ROWS: value rows of the bulk-copy row buffer (0: rows are loaded straight from global memory).
 template <int NG, int NW, int RB_ROWS = 0>
 struct EdgeSmem {
-  static constexpr int SR = (NG <= 4) ? 4 : MAX_GROUP;          // rows of S / red (query heads)
+  static constexpr int SR = (NG <= 4) ? 4 : (NG <= 8) ? 8 : MAX_GROUP;   // rows of S / red (query heads)
   static constexpr int QR = (NG <= 8) ? 8 : MAX_GROUP;          // staged query rows (mma tiles of 8 heads)
   static constexpr int ROWS = RB_ROWS;
   float S[SR][S_ROW];                        // logits, then probabilities

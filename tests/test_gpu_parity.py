@@ -211,6 +211,9 @@ def test_cache_replay_against_oracle_and_reference(kb, name):
     (2, 2, 1, 32 + 4 * 128, torch.float16),      # group of 1
     (1, 16, 1, 32 + 5 * 128 + 3, torch.float16),  # group of 16: two tiles of 8 query heads
     (2, 24, 1, 700, torch.float16),              # group of 12
+    (2, 16, 2, 32 + 7 * 128 + 31, torch.bfloat16),   # group of 8: two full operand groups of the integer kernel
+    (1, 5, 2, 32 + 10 * 128 + 99, torch.float16),    # group of 5: second operand group holds one head
+    (3, 18, 1, 32 + 5 * 128 + 64, torch.bfloat16),   # group of 6
     (1, 4, 2, 20, torch.float16),                # shorter than the sink
     (1, 4, 2, 33, torch.float16),
     (1, 4, 1, 160, torch.float16),               # exactly sink + one page: no packed value page yet
