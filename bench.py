@@ -68,7 +68,7 @@ def parse():
     ap.add_argument("--seq-batch", type=int, default=1, help="seqsplit workload: sequences (the named config has 1)")
     ap.add_argument("--tail-weight", type=int, default=0,
                     help="seqsplit workload: packed pages the last rank's tail is counted as when the pages are split")
-    ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
+    ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer", "step"],
                     help="seqsplit workload: combine the partials with an NCCL all-gather + merge kernel, or inside "
                          "the merge kernel over peer memory")
     return ap.parse_args()
@@ -416,25 +416,29 @@ def seqsplit_measure(kb, device, rank, world, dist, steps, warmup, seq_batch, ex
     NL layers' caches take turns so that every step reads cold pages (NL x 43 MB per sequence > L2) and the steps
     are queued back to back, as the layers of a model are; the same seeds on every rank: same sequences."""
     global H_KV, H_Q
-    from kitty_b200.seqsplit import PartialExchange, seq_split_decode
+    from kitty_b200.seqsplit import PartialExchange, seq_split_decode, seq_split_step
 
     saved = (H_KV, H_Q)
     H_KV, H_Q = 4, 28
     try:
         ctx = 131072
         W, K, SB = max(3, warmup), steps, seq_batch
+        REP = 5                                        # the median of REP repeats of K steps is reported
         NL = 8 if SB * 8 * 43 <= 4000 else 4
-        caches = [build_cache(kb, SB, ctx, (W + K) // NL + 2, device, seed=4321 + j) for j in range(NL)]
+        caches = [build_cache(kb, SB, ctx, (W + REP * K) // NL + 2, device, seed=4321 + j) for j in range(NL)]
         lay = caches[0].kv_cache[0]
         g = torch.Generator(device=device).manual_seed(17)
-        qs = torch.randn(W + K, SB, H_Q, 1, D, generator=g, device=device).to(torch.bfloat16)
-        ks = torch.randn(W + K, SB, H_KV, 1, D, generator=g, device=device).to(torch.bfloat16)
-        vs = torch.randn(W + K, SB, H_KV, 1, D, generator=g, device=device).to(torch.bfloat16)
-        xch = PartialExchange(SB * H_Q, device) if (exchange == "peer" and world > 1) else None
+        qs = torch.randn(W + REP * K, SB, H_Q, 1, D, generator=g, device=device).to(torch.bfloat16)
+        ks = torch.randn(W + REP * K, SB, H_KV, 1, D, generator=g, device=device).to(torch.bfloat16)
+        vs = torch.randn(W + REP * K, SB, H_KV, 1, D, generator=g, device=device).to(torch.bfloat16)
+        xch = PartialExchange(SB * H_Q, device) if (exchange in ("peer", "step") and world > 1) else None
 
         def step(i):
             cache = caches[i % NL]
             layer = cache.kv_cache[0]
+            if exchange == "step":      # one library call per layer step, counters and plan in a device block
+                return seq_split_step(cache, ks[i], vs[i], qs[i], D ** -0.5, rank=rank, world=world, exchange=xch,
+                                      tail_weight=tail_weight)
             cache.update(ks[i], vs[i], 0)
             out = seq_split_decode(qs[i], layer, H_KV, D ** -0.5, rank=rank, world=world,
                                    n_common_pages=layer.PageCount_V, exchange=xch, tail_weight=tail_weight)
@@ -443,23 +447,26 @@ def seqsplit_measure(kb, device, rank, world, dist, steps, warmup, seq_batch, ex
 
         for i in range(W):
             step(i)
-        torch.cuda.synchronize(device)
+        reps = []
+        for r in range(REP):
+            torch.cuda.synchronize(device)
+            if dist is not None and world > 1:
+                dist.barrier()
+            torch.cuda.synchronize(device)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(K):
+                step(W + r * K + i)
+            e1.record()
+            e1.synchronize()
+            reps.append(e0.elapsed_time(e1))
+        t = torch.tensor(reps, device=device, dtype=torch.float64)
         if dist is not None and world > 1:
-            dist.barrier()
-        torch.cuda.synchronize(device)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(K):
-            step(W + i)
-        e1.record()
-        e1.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1)], device=device, dtype=torch.float64)
-        if dist is not None and world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)          # per repeat: the slowest rank
         if xch is not None:
             xch.check()
         packed = SB * H_KV * (lay.PageCount_K * K_PAGE_BYTES + lay.PageCount_V * V_PAGE_BYTES)
-        return float(t[0]) / K * 1e3, packed, NL
+        return float(t.median()) / K * 1e3, packed, NL
     finally:
         H_KV, H_Q = saved
 
@@ -469,18 +476,19 @@ def seqsplit_record(kb, device, rank, world, dist, steps: int = 48, warmup: int 
     partials, next to the same sequence reduced by one GPU alone (rank 0's figure; the other ranks wait)."""
     rec = {"workload": "1 layer step, 28q/4kv heads, 131072 cached tokens, sequence split over the ranks in contiguous "
                        "page ranges; 8 layers' caches in turn (cold pages every step), steps queued back to back; CUDA "
-                       "events, max over ranks", "n_gpus": world, "steps": steps, "unit": "us"}
+                       "events, max over ranks, median of 5 repeats of the steps", "n_gpus": world, "steps": steps,
+           "unit": "us"}
     peak, _ = hbm_peak()
     for sb in (1, 8):
         one = torch.zeros(1, device=device, dtype=torch.float64)
         if rank == 0:
-            us1, packed, _ = seqsplit_measure(kb, device, 0, 1, None, steps, warmup, sb, "nccl", 0)
+            us1, packed, _ = seqsplit_measure(kb, device, 0, 1, None, steps, warmup, sb, "step", 0)
             one[0] = us1
         if world > 1:
             dist.all_reduce(one, op=dist.ReduceOp.MAX)
         us1 = float(one[0])
         r = {"one_gpu_us": us1}
-        for ex in ("peer", "nccl"):
+        for ex in ("step", "peer", "nccl"):
             us, packed, _ = seqsplit_measure(kb, device, rank, world, dist, steps, warmup, sb, ex, 0)
             r[f"{ex}_us"] = us
             r[f"{ex}_speedup_vs_one_gpu"] = us1 / us
@@ -489,7 +497,10 @@ def seqsplit_record(kb, device, rank, world, dist, steps: int = 48, warmup: int 
         r["packed_kv_bytes"] = packed
         r["one_gpu_frac_of_peak"] = packed / (us1 * 1e-6) / 1e9 / peak
         rec[f"batch{sb}"] = r
-    rec["collective"] = {"peer": "none: the attention call's merge step stores the partials into every rank's buffer over "
+    rec["collective"] = {"step": "none: as 'peer', with the whole layer step (append, attention, exchange, flush) in one "
+                                 "library call from device-resident counters (kitty_decode_step_exchange); the "
+                                 "one-GPU figure uses the same one-call step (kitty_decode_step)",
+                         "peer": "none: the attention call's merge step stores the partials into every rank's buffer over "
                                  "NVLink and waits (bounded) for the others (kitty_decode_attn_exchange)",
                          "nccl": "all_gather of [28,130] fp32 per rank + kitty_lse_merge"}
     return rec
@@ -516,8 +527,9 @@ def seqsplit_workload(args):
                           "config": {"workload": f"1 layer, 28q/4kv heads, batch {args.seq_batch}, 131072 cached tokens, "
                                                  f"sequence split over {world} GPU(s) (tail weight {args.tail_weight}), "
                                                  f"{NL} layers' caches in turn (cold pages every step), steps queued back to back",
-                                     "collective": "peer-memory exchange inside the attention call" if args.exchange == "peer"
-                                     and world > 1 else "all_gather of [28,130] fp32 per rank + merge"}}))
+                                     "collective": "peer-memory exchange inside the attention call" if args.exchange != "nccl"
+                                     and world > 1 else "all_gather of [28,130] fp32 per rank + merge",
+                                     "calls_per_step": 1 if args.exchange == "step" else 3}}))
     if dist is not None:
         dist.destroy_process_group()
 

@@ -177,12 +177,13 @@ int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *counts, cons
  *
  *   host, once per token:   kitty_plan_step(...) fills a kitty_step_state on the host and
  *                           writes it to the device block (one small launch on the stream: the
- *                           160 bytes travel as a kernel argument, so no host buffer has to
+ *                           168 bytes travel as a kernel argument, so no host buffer has to
  *                           stay untouched until the copy runs).
  *   per layer (capturable): kitty_decode_step(...) = append + attention + merge + flush-if-due.
  *   host, after the token:  advance the counters as kvcache/kitty.py:102-123, 201-234 does
  *                           (kitty_plan_step returns the new counters in state->next).
- * Limits: whole sequence on one GPU, in-kernel channel selection. */
+ * Limits: in-kernel channel selection.  kitty_plan_step / kitty_decode_step cover the whole sequence on one
+ * GPU; the _split / _exchange forms below cover this rank's part of a sequence split over GPUs. */
 typedef struct {
   kitty_counts before;   /* state before this step's append                                        */
   kitty_counts after;    /* after the append: what the attention kernels see                       */
@@ -190,12 +191,21 @@ typedef struct {
   int32_t pb, pe, ch, nchunk, has_sink, has_tail, n_slots, n_tiles, chunk_slot0, edge_slot;
   int32_t n_items, n_edge, flush_k, flush_v;
   int32_t edge_parts, edge_part_tok;
-} kitty_step_state;      /* 160 bytes */
+  int32_t xchg_seq, reserved;      /* sequence-split steps: exchange sequence number of the step's first layer */
+} kitty_step_state;      /* 168 bytes */
 
 /* Fills *state (host memory) for one decode step of a cache whose counters are *before and, when
  * device_state is not null, stores the same 160 bytes there in stream order. */
 int kitty_plan_step(const kitty_layer *layer, const kitty_counts *before, int32_t B, int32_t h_q,
                     kitty_step_state *state, kitty_step_state *device_state, void *stream);
+
+/* kitty_plan_step for one rank of a sequence split over GPUs: the attention of the step visits the common packed
+ * pages [page_begin, page_end) only, flags as for kitty_decode_attn (bit0 sink, bit1 tail), and xchg_seq is the
+ * exchange sequence number of the step's first layer (see kitty_decode_step_exchange).  The append and the flushes
+ * are planned as in kitty_plan_step: every rank keeps the counters (and, cheaply, the fp16 buffers) up to date. */
+int kitty_plan_step_split(const kitty_layer *layer, const kitty_counts *before, int32_t B, int32_t h_q,
+                          int32_t page_begin, int32_t page_end, int32_t flags, int32_t xchg_seq,
+                          kitty_step_state *state, kitty_step_state *device_state, void *stream);
 
 /* One layer's decode step from the device-resident state: kitty_append, kitty_decode_attn
  * (impl 0, whole sequence) and kitty_flush in four launches whose arguments do not depend on the
@@ -206,6 +216,18 @@ int kitty_decode_step(const kitty_layer *layer, const kitty_step_state *device_s
                       const void *value, int kv_dtype, int64_t k_stride_b, int64_t k_stride_h, int64_t v_stride_b,
                       int64_t v_stride_h, const void *query, int q_dtype, int32_t B, int32_t h_q, float scaling,
                       void *out, int out_dtype, void *workspace, int64_t workspace_bytes, int div_mode, void *stream);
+
+/* kitty_decode_step for one rank of a sequence split: the merge step of the attention exchanges this rank's partial
+ * with the other ranks over peer memory and writes the complete result, as kitty_decode_attn_exchange does (same
+ * exchange buffers, same bounded waits).  The sequence number of the exchange is device_state->xchg_seq +
+ * seq_offset, so that the launch arguments do not change from token to token: give every layer of a model its own
+ * seq_offset (0, 1, 2, ...) and let xchg_seq grow by the number of layers per token, starting at 1. */
+int kitty_decode_step_exchange(const kitty_layer *layer, const kitty_step_state *device_state, const void *key,
+                               const void *value, int kv_dtype, int64_t k_stride_b, int64_t k_stride_h,
+                               int64_t v_stride_b, int64_t v_stride_h, const void *query, int q_dtype, int32_t B,
+                               int32_t h_q, float scaling, void *out, int out_dtype, void *workspace,
+                               int64_t workspace_bytes, int div_mode, void *const *peer_buffers, int32_t rank,
+                               int32_t world, int32_t seq_offset, int32_t *status, int64_t wait_ns, void *stream);
 
 /* Size in bytes of the scratch array built into the library for kitty_decode_attn_static. */
 #define KITTY_STATIC_SCRATCH_BYTES (8u << 20)

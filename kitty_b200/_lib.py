@@ -23,6 +23,7 @@ EXPORTS = [
     "kitty_append", "kitty_flush", "kitty_decode_workspace_bytes", "kitty_workspace_status", "kitty_decode_attn",
     "kitty_lse_merge", "kitty_decode_attn_static", "kitty_plan_step", "kitty_decode_step",
     "kitty_lse_exchange_bytes", "kitty_lse_exchange_merge", "kitty_decode_attn_exchange", "kitty_rope_qk",
+    "kitty_plan_step_split", "kitty_decode_step_exchange",
 ]
 
 
@@ -47,7 +48,7 @@ class KittyStepState(C.Structure):
     _fields_ = [("before", KittyCounts), ("after", KittyCounts), ("next", KittyCounts)] + \
                [(n, C.c_int32) for n in ("pb", "pe", "ch", "nchunk", "has_sink", "has_tail", "n_slots", "n_tiles",
                                          "chunk_slot0", "edge_slot", "n_items", "n_edge", "flush_k", "flush_v",
-                                         "edge_parts", "edge_part_tok")]
+                                         "edge_parts", "edge_part_tok", "xchg_seq", "reserved")]
 
 
 class KittyError(RuntimeError):
@@ -104,6 +105,13 @@ def lib() -> C.CDLL:
     L.kitty_decode_step.restype = C.c_int
     L.kitty_decode_step.argtypes = [C.POINTER(KittyLayer), vp, vp, vp, C.c_int, i64, i64, i64, i64, vp, C.c_int, i32,
                                     i32, C.c_float, vp, C.c_int, vp, i64, C.c_int, vp]
+    L.kitty_plan_step_split.restype = C.c_int
+    L.kitty_plan_step_split.argtypes = [C.POINTER(KittyLayer), C.POINTER(KittyCounts), i32, i32, i32, i32, i32, i32,
+                                        C.POINTER(KittyStepState), vp, vp]
+    L.kitty_decode_step_exchange.restype = C.c_int
+    L.kitty_decode_step_exchange.argtypes = [C.POINTER(KittyLayer), vp, vp, vp, C.c_int, i64, i64, i64, i64, vp, C.c_int,
+                                             i32, i32, C.c_float, vp, C.c_int, vp, i64, C.c_int, vp, i32, i32, i32, vp,
+                                             i64, vp]
     L.kitty_decode_attn_exchange.restype = C.c_int
     L.kitty_decode_attn_exchange.argtypes = [C.POINTER(KittyLayer), C.POINTER(KittyCounts), vp, C.c_int, i32, i32,
                                              C.c_float, vp, C.c_int, vp, i64, i32, i32, i32, C.c_int, vp, i32, i32, i32,

@@ -45,6 +45,7 @@ class KittyCache(Cache):
         self.fuse_eager_steps = True      # patched attention modules use plan_step/step_layer/finish_step for decode tokens
         self._step_dev: Optional[torch.Tensor] = None       # device block of the device-resident decode step
         self._step_host = None
+        self._step_exchange = None                          # seqsplit.PartialExchange of the token being planned
         self.kv_cache: list[KVCache_Layer] = [
             KVCache_Layer(MAX_BS=max_batch_size, MAX_LEN=max_length, H_KV=self.num_key_value_heads, D=self.head_dim,
                           D_BOOSTED=self.d_boosted, LOW_BIT=self.low_bit, HIGH_BIT=self.high_bit,
@@ -174,7 +175,11 @@ class KittyCache(Cache):
     #     cache.step_layer(i, k, v, q, ...)  per layer; four launches with step-independent arguments
     #     cache.finish_step()                host, once per token: counters := state after the flushes
     # step_layer may be captured in a CUDA graph and replayed for every later token.
-    def plan_step(self, batch: int, h_q: int) -> "_lib.KittyStepState":
+    def plan_step(self, batch: int, h_q: int, page_begin: int = 0, page_end: int = -1, flags: int = 3,
+                  exchange=None) -> "_lib.KittyStepState":
+        """Plan one decode token.  page_begin / page_end / flags select this rank's part of a sequence split over
+        GPUs (defaults: the whole sequence); with `exchange` (a seqsplit.PartialExchange) the layers' step_layer
+        calls of this token combine the ranks' partials over peer memory, one exchange per layer."""
         import ctypes
 
         if self.selection != "fused":
@@ -188,10 +193,16 @@ class KittyCache(Cache):
         if self._step_dev is None:
             self._step_dev = torch.zeros(ctypes.sizeof(_lib.KittyStepState), dtype=torch.uint8, device=lay0.device)
         st = _lib.KittyStepState()
-        rc = _lib.lib().kitty_plan_step(lay0.c_layer(), lay0.c_counts(), batch, h_q, ctypes.byref(st),
-                                        self._step_dev.data_ptr(), _lib.stream_ptr(lay0.device))
-        _lib.check(rc, "kitty_plan_step")
+        seq0 = 0
+        if exchange is not None:
+            seq0 = exchange.seq + 1                      # layer i of this token uses sequence number seq0 + i
+            exchange.seq += self.num_hidden_layers
+        rc = _lib.lib().kitty_plan_step_split(lay0.c_layer(), lay0.c_counts(), batch, h_q, page_begin, page_end, flags,
+                                              seq0, ctypes.byref(st), self._step_dev.data_ptr(),
+                                              _lib.stream_ptr(lay0.device))
+        _lib.check(rc, "kitty_plan_step_split")
         self._step_host = st
+        self._step_exchange = exchange
         return st
 
     def step_layer(self, layer_idx: int, key_states: torch.Tensor, value_states: torch.Tensor, query: torch.Tensor,
@@ -208,13 +219,20 @@ class KittyCache(Cache):
         if out is None:
             out = torch.empty((B, 1, H_Q, D), dtype=query.dtype, device=query.device)
         ws = lay.workspace(lay.MAX_BS, H_Q)
-        rc = _lib.lib().kitty_decode_step(lay.c_layer(), self._step_dev.data_ptr(), key_states.data_ptr(),
-                                          value_states.data_ptr(), _lib.dtype_code(key_states.dtype),
-                                          key_states.stride(0), key_states.stride(1), value_states.stride(0),
-                                          value_states.stride(1), query.data_ptr(), _lib.dtype_code(query.dtype), B,
-                                          H_Q, float(scaling), out.data_ptr(), _lib.dtype_code(out.dtype),
-                                          ws.data_ptr(), ws.numel(), self.div_mode, _lib.stream_ptr(query.device))
-        _lib.check(rc, "kitty_decode_step")
+        args = (lay.c_layer(), self._step_dev.data_ptr(), key_states.data_ptr(), value_states.data_ptr(),
+                _lib.dtype_code(key_states.dtype), key_states.stride(0), key_states.stride(1), value_states.stride(0),
+                value_states.stride(1), query.data_ptr(), _lib.dtype_code(query.dtype), B, H_Q, float(scaling),
+                out.data_ptr(), _lib.dtype_code(out.dtype), ws.data_ptr(), ws.numel(), self.div_mode)
+        xch = getattr(self, "_step_exchange", None)
+        if xch is None:
+            rc = _lib.lib().kitty_decode_step(*args, _lib.stream_ptr(query.device))
+            _lib.check(rc, "kitty_decode_step")
+        else:
+            assert B * H_Q == xch.rows
+            rc = _lib.lib().kitty_decode_step_exchange(*args, xch.peer_table, xch.rank, xch.world, layer_idx,
+                                                       xch.status.data_ptr(), xch.wait_ns,
+                                                       _lib.stream_ptr(query.device))
+            _lib.check(rc, "kitty_decode_step_exchange")
         return out
 
     def finish_step(self) -> None:
@@ -228,6 +246,7 @@ class KittyCache(Cache):
             lay.Local_Count_V, lay.Write_Offset_Local_V = n.Local_Count_V, n.Write_Offset_Local_V
             lay.ensure_pages(lay.PageCount_K + 1, lay.PageCount_V + 1)
         self._step_host = None
+        self._step_exchange = None
 
     @staticmethod
     def _counter_tuple(lay) -> tuple:

@@ -9,6 +9,7 @@ namespace kitty {
 
 constexpr int64_t WS_HEADER = 256;   // bytes at the start of the workspace: sticky status word, item hand-out counter
 constexpr int PG_WARPS_HOST = 4;     // warps per block of the streaming kernel (pages per chunk come in multiples)
+constexpr int MAX_CHUNKS = 128;      // chunks per (batch, kv-head): with few rows, one page per warp fills the GPU
 
 }  // namespace kitty
 
@@ -28,7 +29,7 @@ namespace kitty {
 
 static int chunk_cap(int64_t bh_gt, int grid_max) {
   const int64_t cap = (16LL * grid_max) / std::max<int64_t>(1, bh_gt);
-  return static_cast<int>(std::min<int64_t>(64, std::max<int64_t>(1, cap)));
+  return static_cast<int>(std::min<int64_t>(MAX_CHUNKS, std::max<int64_t>(1, cap)));
 }
 
 // Pick pages-per-chunk so that the items fill `grid_max` resident blocks in whole waves.
@@ -47,10 +48,15 @@ static void plan_chunks(int n_pages, int64_t bh_gt, int grid_max, bool dynamic, 
     const int n = (n_pages + ch - 1) / ch;
     const int64_t items = bh_gt * n;
     const int64_t waves = (items + grid_max - 1) / grid_max;
-    const double item_cost = ch / PG_WARPS_HOST + 1.5;                              // +1.5: per-item prologue/merge
-    // static round-robin: whole waves; dynamic hand-out: average load plus one item of tail
-    const double cost = dynamic ? (static_cast<double>(items) * item_cost / grid_max + item_cost)
-                                : static_cast<double>(waves) * item_cost;
+    // per item: its pages (one per warp at a time) plus a fixed part worth about 2.5 pages — the table look-up, the
+    // first copy's flight, the block's merge
+    const double item_cost = ch / PG_WARPS_HOST + 2.5;
+    // static round-robin: whole waves.  Dynamic hand-out: the average load plus one item of tail — except for a
+    // small call (latency-bound: every item has a block of its own and a warp walks at most four pages), which
+    // takes one item's time
+    const bool one_wave = items <= grid_max && ch <= 4 * PG_WARPS_HOST;
+    const double cost = !dynamic ? static_cast<double>(waves) * item_cost
+                        : (one_wave ? item_cost : static_cast<double>(items) * item_cost / grid_max + item_cost);
     if (cost < best - 1e-9) {
       best = cost;
       best_ch = ch;
@@ -90,7 +96,7 @@ extern "C" int64_t kitty_decode_workspace_bytes(int32_t B, int32_t h_kv, int32_t
   const int64_t bh = static_cast<int64_t>(B) * h_kv;
   // chunk slots of a call with bh' <= bh rows: bh' * min(chunk_cap(bh'), pages / 4) <= the expression below, which
   // never decreases with bh — a workspace sized for the largest batch serves every smaller one
-  const int64_t cap_pages = std::min<int64_t>(64, std::max(1, (max_pages + PG_WARPS_HOST - 1) / PG_WARPS_HOST));
+  const int64_t cap_pages = std::min<int64_t>(MAX_CHUNKS, std::max(1, (max_pages + PG_WARPS_HOST - 1) / PG_WARPS_HOST));
   const int64_t chunk_slots = std::min(bh * cap_pages, std::max(bh, 16 * grid_max));
   return WS_HEADER + (chunk_slots + bh * EDGE_PARTS_MAX) * G * PART * static_cast<int64_t>(sizeof(float));
 }
@@ -170,7 +176,10 @@ static int decode_attn_core(const kitty_layer *layer, const kitty_counts *counts
     const int64_t n_edge = static_cast<int64_t>(B) * H * P.edge_parts;
     if (items + n_edge > 0) {
       const int grid = static_cast<int>(std::min<int64_t>(items + n_edge, grid_max));
-      if (int rc = launch_decode_paged_i8(a, static_cast<int>(items), static_cast<int>(n_edge), grid, s)) return rc;
+      // launched as a programmatic dependent of whatever precedes it in the stream (the kernel waits for that work
+      // before it reads anything): behind kitty_append, whose blocks release their dependents at once, the launch
+      // latency of this kernel is hidden
+      if (int rc = launch_decode_paged_i8(a, static_cast<int>(items), static_cast<int>(n_edge), grid, s, true)) return rc;
     }
   } else if (P.fast_chunks) {
     // the fp16 streaming kernel reduces the edge parts in its own grid too, after a block's page items
@@ -278,7 +287,13 @@ __global__ void store_step_state_kernel(kitty_step_state st, kitty_step_state *d
 
 extern "C" int kitty_plan_step(const kitty_layer *layer, const kitty_counts *before, int32_t B, int32_t h_q,
                                kitty_step_state *state, kitty_step_state *device_state, void *stream) {
-  if (!layer || !before || !state) return KITTY_E_BADARG;
+  return kitty_plan_step_split(layer, before, B, h_q, 0, -1, 3, 0, state, device_state, stream);
+}
+
+extern "C" int kitty_plan_step_split(const kitty_layer *layer, const kitty_counts *before, int32_t B, int32_t h_q,
+                                     int32_t page_begin, int32_t page_end, int32_t flags, int32_t xchg_seq,
+                                     kitty_step_state *state, kitty_step_state *device_state, void *stream) {
+  if (!layer || !before || !state || xchg_seq < 0) return KITTY_E_BADARG;
   if (layer->head_dim != HD || layer->page_size != PAGE || layer->d_boost != DB || layer->sink_size != SINK)
     return KITTY_E_BADSHAPE;
   const int H = layer->h_kv;
@@ -317,18 +332,19 @@ extern "C" int kitty_plan_step(const kitty_layer *layer, const kitty_counts *bef
   // plan of the attention call (whole sequence, int8 streaming kernel)
   const int pv = c.PageCount_V;
   const int64_t tk = static_cast<int64_t>(c.PageCount_K) * PAGE + c.Q_Buffer_Count_K;
-  st.pb = 0;
-  st.pe = pv;
+  st.pb = std::min(std::max(page_begin, 0), pv);
+  st.pe = page_end < 0 ? pv : std::min(std::max(page_end, st.pb), pv);
   st.n_tiles = 1 + static_cast<int>((tk + PAGE - 1) / PAGE);
-  st.has_sink = c.Sink_Count > 0 ? 1 : 0;
-  st.has_tail = (st.n_tiles - 1 - pv) > 0 ? 1 : 0;
+  st.has_sink = ((flags & 1) && c.Sink_Count > 0) ? 1 : 0;
+  st.has_tail = ((flags & 2) && (st.n_tiles - 1 - pv) > 0) ? 1 : 0;
+  st.xchg_seq = xchg_seq;
   // the same plan kitty_decode_attn makes for these counters: int8 kernel for groups of up to 8 heads, fp16 kernel above
   const bool use_i8 = G <= 8;
   const int n_gt = use_i8 ? 1 : (G + 7) / 8;
   const int grid_max = (use_i8 ? i8_blocks_per_sm(G) : 2) * sm_count();
   plan_edge(st.has_sink, st.has_tail, c, static_cast<int64_t>(B) * H, true, &st.edge_parts, &st.edge_part_tok);
   const int64_t edge_blocks = use_i8 ? 0 : std::min<int64_t>(static_cast<int64_t>(B) * H * st.edge_parts, grid_max / 2);
-  plan_chunks(pv, static_cast<int64_t>(B) * H * n_gt, grid_max - static_cast<int>(edge_blocks), use_i8, &st.ch, &st.nchunk);
+  plan_chunks(st.pe - st.pb, static_cast<int64_t>(B) * H * n_gt, grid_max - static_cast<int>(edge_blocks), use_i8, &st.ch, &st.nchunk);
   st.n_slots = st.edge_parts + st.nchunk;
   st.chunk_slot0 = st.edge_parts;
   st.edge_slot = 0;
@@ -342,11 +358,11 @@ extern "C" int kitty_plan_step(const kitty_layer *layer, const kitty_counts *bef
   return KITTY_OK;
 }
 
-extern "C" int kitty_decode_step(const kitty_layer *layer, const kitty_step_state *device_state, const void *key,
-                                 const void *value, int kv_dtype, int64_t k_stride_b, int64_t k_stride_h,
-                                 int64_t v_stride_b, int64_t v_stride_h, const void *query, int q_dtype, int32_t B,
-                                 int32_t h_q, float scaling, void *out, int out_dtype, void *workspace,
-                                 int64_t workspace_bytes, int div_mode, void *stream) {
+static int decode_step_core(const kitty_layer *layer, const kitty_step_state *device_state, const void *key,
+                            const void *value, int kv_dtype, int64_t k_stride_b, int64_t k_stride_h,
+                            int64_t v_stride_b, int64_t v_stride_h, const void *query, int q_dtype, int32_t B,
+                            int32_t h_q, float scaling, void *out, int out_dtype, void *workspace,
+                            int64_t workspace_bytes, int div_mode, const XchgDesc *xchg, void *stream) {
   if (!layer || !device_state || !key || !value || !query || !out || !workspace) return KITTY_E_BADARG;
   if (layer->head_dim != HD || layer->page_size != PAGE || layer->d_boost != DB || layer->sink_size != SINK)
     return KITTY_E_BADSHAPE;
@@ -399,9 +415,44 @@ extern "C" int kitty_decode_step(const kitty_layer *layer, const kitty_step_stat
   m.partial_out = nullptr;
   m.work_counter = a.status + 1;
   m.dyn = device_state;
-  m.x = XchgDesc{};
-  if (int rc = launch_merge(m, s)) return rc;
+  m.x = xchg ? *xchg : XchgDesc{};      // with an exchange, x.seq is the layer's offset to the state's sequence number
+  if (int rc = launch_merge(m, s)) {
+    cudaMemsetAsync(a.status + 1, 0, sizeof(int32_t), s);      // see decode_attn_core
+    return rc;
+  }
   return launch_flush_dyn(*layer, device_state, B, div_mode, s);
+}
+
+extern "C" int kitty_decode_step(const kitty_layer *layer, const kitty_step_state *device_state, const void *key,
+                                 const void *value, int kv_dtype, int64_t k_stride_b, int64_t k_stride_h,
+                                 int64_t v_stride_b, int64_t v_stride_h, const void *query, int q_dtype, int32_t B,
+                                 int32_t h_q, float scaling, void *out, int out_dtype, void *workspace,
+                                 int64_t workspace_bytes, int div_mode, void *stream) {
+  return decode_step_core(layer, device_state, key, value, kv_dtype, k_stride_b, k_stride_h, v_stride_b, v_stride_h, query,
+                          q_dtype, B, h_q, scaling, out, out_dtype, workspace, workspace_bytes, div_mode, nullptr, stream);
+}
+
+extern "C" int kitty_decode_step_exchange(const kitty_layer *layer, const kitty_step_state *device_state, const void *key,
+                                          const void *value, int kv_dtype, int64_t k_stride_b, int64_t k_stride_h,
+                                          int64_t v_stride_b, int64_t v_stride_h, const void *query, int q_dtype,
+                                          int32_t B, int32_t h_q, float scaling, void *out, int out_dtype,
+                                          void *workspace, int64_t workspace_bytes, int div_mode,
+                                          void *const *peer_buffers, int32_t rank, int32_t world, int32_t seq_offset,
+                                          int32_t *status, int64_t wait_ns, void *stream) {
+  if (!peer_buffers || world <= 0 || world > 128 || rank < 0 || rank >= world || seq_offset < 0 || wait_ns < 0)
+    return KITTY_E_BADARG;
+  const int64_t rows = static_cast<int64_t>(B) * h_q;
+  if (rows <= 0 || rows > KITTY_EXCHANGE_MAX_ROWS) return KITTY_E_BADARG;
+  XchgDesc x;
+  x.peers = reinterpret_cast<float *const *>(peer_buffers);
+  kitty_lse_exchange_bytes(rows, world, &x.flag_offset);
+  x.rank = rank;
+  x.world = world;
+  x.seq = seq_offset;
+  x.status = status;
+  x.wait_ns = wait_ns > 0 ? static_cast<unsigned long long>(wait_ns) : XCHG_WAIT_NS_DEFAULT;
+  return decode_step_core(layer, device_state, key, value, kv_dtype, k_stride_b, k_stride_h, v_stride_b, v_stride_h, query,
+                          q_dtype, B, h_q, scaling, out, out_dtype, workspace, workspace_bytes, div_mode, &x, stream);
 }
 
 extern "C" int kitty_workspace_status(const void *workspace, int32_t *host_status, void *stream) {

@@ -224,26 +224,27 @@ __global__ void __launch_bounds__(I8_WARPS * 32, NG == 1 ? 4 : 3) decode_paged_i
   uint32_t inflight = 0;     // bit 0: a key-part copy is in flight, bit 1: a value-part copy (warp-uniform)
   const uint32_t bar_k = smem_u32(&smem.bar_k[warp]), bar_v = smem_u32(&smem.bar_v[warp]), stage_u32 = smem_u32(&ws.stage[0]);
 
-  // Items are handed out dynamically (a work counter in the workspace header, zero on entry and reset by
-  // the merge kernel that always follows), so blocks stay busy until the list is empty.  Edge items are
-  // spread evenly through the sequence (position i holds an edge item when floor((i+1)*n_edge/total) >
-  // floor(i*n_edge/total)): at any time most blocks stream pages while a few reduce a latency-bound edge.
+  // Items: a block's first item is its own index; further items are handed out by a work counter in the workspace
+  // header (zero on entry, reset by the merge kernel that always follows), so blocks stay busy until the list is
+  // empty.  The counter is bumped at the START of an item and its result picked up at the end, which hides the
+  // round trip of the atomic.  Edge items are spread evenly through the sequence (position i holds an edge item
+  // when floor((i+1)*n_edge/total) > floor(i*n_edge/total)): at any time most blocks stream pages while a few
+  // reduce a latency-bound edge.
   const long long total = static_cast<long long>(n_items) + n_edge;
-  for (;;) {
-    __syncthreads();     // the previous item's merge buffer, query and work index are no longer read
-    if (tid == 0) smem.next_item = atomicAdd(a.status + 1, 1);
-    __syncthreads();
-    const int it = smem.next_item;
-    if (it >= total) break;
-    const int e_before = static_cast<int>(static_cast<long long>(it) * n_edge / total);
-    const int e_after = static_cast<int>((static_cast<long long>(it) + 1) * n_edge / total);
-    const int item = it - e_before;        // index among the page-pair items
+  for (long long it = blockIdx.x; it < total; it = smem.next_item) {
+    int it_next = 0;
+    if (tid == 0) it_next = atomicAdd(a.status + 1, 1) + static_cast<int>(gridDim.x);
+    const int e_before = static_cast<int>(it * n_edge / total);
+    const int e_after = static_cast<int>((it + 1) * n_edge / total);
+    const int item = static_cast<int>(it) - e_before;        // index among the page-pair items
     if (e_after > e_before) {
       // ---- edge item: one part of the sink + tail of one (batch, kv-head), by the whole block ---- //
       const int ebh = e_before / P.edge_parts, part = e_before % P.edge_parts;
       edge_item<4 * NG, I8_WARPS>(a, P, C, smem.u.e, ebh / H, ebh % H, part, smem_u32(&smem.bar_e), &edge_phase);
       __syncthreads();
       ws.inv[lane] = 0;  // the slot table was overwritten: keep its entries valid positions
+      if (tid == 0) smem.next_item = it_next;
+      __syncthreads();   // the edge buffers are no longer read; the next item's index is visible
       continue;
     }
     const int c = item % P.nchunk;
@@ -252,6 +253,18 @@ __global__ void __launch_bounds__(I8_WARPS * 32, NG == 1 ? 4 : 3) decode_paged_i
     const int p0 = P.pb + c * P.ch;
     const int p1 = min(P.pe, p0 + P.ch);
 
+    // this warp's pages: p0 + warp, p0 + warp + I8_WARPS, ...  (requested first: the copies fly while the
+    // query is staged)
+    const int first = p0 + warp;
+    if (!dead && first < p1) {
+      if (lane == 0) {
+        // the stage may have been written through the generic proxy (merge buffer): order that before the bulk copies
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        i8_issue_k(a, h, a.L.PageTable_K[static_cast<int64_t>(b) * a.L.max_page + first], stage_u32, bar_k);
+        i8_issue_v(a, h, a.L.PageTable_V[static_cast<int64_t>(b) * a.L.max_page + first], stage_u32, bar_v);
+      }
+      inflight = 3u;
+    }
     // ---- queries of heads warp, warp + 4, ...: maximum, then q / qmax ---- //
 #pragma unroll
     for (int g = 0; g < NG; ++g) {
@@ -270,17 +283,6 @@ __global__ void __launch_bounds__(I8_WARPS * 32, NG == 1 ? 4 : 3) decode_paged_i
       *reinterpret_cast<float4 *>(&sm.qarr[hq][4 * lane]) =
           make_float4(qv[0] * inv_mx, qv[1] * inv_mx, qv[2] * inv_mx, qv[3] * inv_mx);
       if (lane == 0) sm.qmax[hq] = mx;
-    }
-    // this warp's pages: p0 + warp, p0 + warp + I8_WARPS, ...
-    const int first = p0 + warp;
-    if (!dead && first < p1) {
-      if (lane == 0) {
-        // the stage may have been written through the generic proxy (merge buffer): order that before the bulk copies
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        i8_issue_k(a, h, a.L.PageTable_K[static_cast<int64_t>(b) * a.L.max_page + first], stage_u32, bar_k);
-        i8_issue_v(a, h, a.L.PageTable_V[static_cast<int64_t>(b) * a.L.max_page + first], stage_u32, bar_v);
-      }
-      inflight = 3u;
     }
     __syncthreads();   // staged query visible
 
@@ -591,6 +593,8 @@ __global__ void __launch_bounds__(I8_WARPS * 32, NG == 1 ? 4 : 3) decode_paged_i
         }
       }
     }
+    if (tid == 0) smem.next_item = it_next;
+    __syncthreads();     // the merge buffer and the query are no longer read; the next item's index is visible
   }
 }
 

@@ -202,7 +202,10 @@ __global__ void __launch_bounds__(128 * MERGE_GROUPS) merge_kernel(MergeArgs a) 
   const int lane = threadIdx.x & 31, warp = (threadIdx.x >> 5) & 3;
   dep_wait();          // launched while the kernel that writes the partials may still be running
   dep_release();       // a flush launched behind this kernel may be scheduled; it waits for this grid to complete
-  if (a.dyn != nullptr) a.n = a.ns = a.dyn->n_slots;
+  if (a.dyn != nullptr) {
+    a.n = a.ns = a.dyn->n_slots;
+    a.x.seq += a.dyn->xchg_seq;        // device-resident step: x.seq holds the layer's offset
+  }
   const float *base = a.partials + ((r / a.gm) * a.ns * a.gm + r % a.gm) * PART;
   float M = -INFINITY, A = 0.f, Lsum = 0.f;
   for (int s0 = 0; s0 < a.n; s0 += 128) {           // chunks of 128 slots (one chunk in practice)

@@ -171,3 +171,21 @@ def seq_split_decode(query: torch.Tensor, layer, num_kv_heads: int, scaling: flo
         flat.copy_(part)
     parts = flat.view((world,) + tuple(part.shape))
     return (merge_fn or _cuda_merge)(parts, query.dtype)
+
+
+def seq_split_step(cache, key_states: torch.Tensor, value_states: torch.Tensor, query: torch.Tensor, scaling: float, *,
+                   rank: int, world: int, exchange: Optional[PartialExchange], layer_idx: int = 0,
+                   tail_weight: int = 0) -> torch.Tensor:
+    """One decode token of a single-layer cache on one rank of a sequence split, in ONE library call per layer:
+    append + this rank's part of the attention + exchange of the partials over peer memory + flush-if-due, all from
+    the device-resident step state (KittyCache.plan_step / step_layer / finish_step).  Every rank holds the
+    counters and the small fp16 buffers; packed pages are only read inside the rank's own range.  With world == 1
+    (exchange None) it is the ordinary one-call step.  For a model, call plan_step once per token and step_layer per
+    layer instead."""
+    lay = cache.kv_cache[layer_idx]
+    lo, hi = split_pages(lay.PageCount_V, world, tail_weight)[rank]
+    cache.plan_step(query.shape[0], query.shape[1], page_begin=lo, page_end=hi, flags=rank_flags(rank, world),
+                    exchange=exchange if world > 1 else None)
+    out = cache.step_layer(layer_idx, key_states, value_states, query, scaling)
+    cache.finish_step()
+    return out

@@ -58,7 +58,32 @@ def _worker(rank, world, port, q_out):
         torch.cuda.synchronize(dev)
         err_x = max(err_x, (out_y.float() - out.float()).abs().max().item() / out.float().abs().max().item())
     xch.check()
-    q_out.put((rank, err, err_x))
+    # the whole layer step in one call per rank (device-resident counters, exchange inside): same tokens appended on
+    # every rank, results equal to the three-call path on a twin cache, through a flush
+    from kitty_b200.seqsplit import seq_split_step
+
+    twin = kb.KittyCache(cfg, B, L + 64, device=dev)
+    step_cache = kb.KittyCache(cfg, B, L + 64, device=dev)
+    for c in (twin, step_cache):
+        c.update(k.to(dev), v.to(dev), 0)
+        c.quantize_prefill(0)
+    err_s = 0.0
+    for s_ in range(90):                                   # the Q-buffers hold 50 tokens: a key flush at step 78
+        kt = torch.randn(B, h_kv, 1, 128, generator=g).bfloat16().to(dev)
+        vt = torch.randn(B, h_kv, 1, 128, generator=g).bfloat16().to(dev)
+        qt = torch.randn(B, h_q, 1, 128, generator=g).bfloat16().to(dev)
+        twin.update(kt, vt, 0)
+        want = kb.decode_attention(qt, twin.kv_cache[0], h_kv, 128 ** -0.5)
+        twin.quantize_decode(0)
+        got = seq_split_step(step_cache, kt, vt, qt, 128 ** -0.5, rank=rank, world=world, exchange=xch)
+        if s_ % 11 == 0 or s_ > 75:
+            torch.cuda.synchronize(dev)
+            err_s = max(err_s, (got.float() - want.float()).abs().max().item() / want.float().abs().max().item())
+    torch.cuda.synchronize(dev)
+    xch.check()
+    assert step_cache.kv_cache[0].PageCount_K == twin.kv_cache[0].PageCount_K == 41
+    assert torch.equal(step_cache.kv_cache[0].KeyCache, twin.kv_cache[0].KeyCache)
+    q_out.put((rank, err, max(err_x, err_s)))
     dist.barrier()
     dist.destroy_process_group()
 
