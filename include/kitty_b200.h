@@ -168,6 +168,29 @@ int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *counts, cons
                       int64_t workspace_bytes, int32_t page_begin, int32_t page_end, int32_t flags,
                       float *partial_out, int impl, void *stream);
 
+/* ---- Ragged batches: one set of counters per batch row -------------------------------------
+ * The reference keeps ONE set of counters for the whole batch (utils_kv_per_layer.py:53-80), so every sequence of a
+ * batch has to have the same length and a prompt can only be given in one piece (kvcache/kitty.py:89-95).  These
+ * entry points take a kitty_counts per batch row instead — the same structure twice: row_counts_host (host memory,
+ * B entries: argument checks and the work plan) and row_counts_dev (device memory, B entries, the same values: read
+ * by the kernels).  The caller advances every row's counters as kvcache/kitty.py:102-123 and :201-234 do for the
+ * batch.  Rows may then differ in length, and a prompt can arrive in several pieces (token by token through
+ * kitty_append_rows / kitty_flush_rows).
+ *
+ * kitty_append_rows: kitty_append per row; a row whose `reserved` field is non-zero takes no token in this call.
+ * kitty_flush_rows:  kitty_flush per row: a row's Q_Buffer_K / Q_Buffer_V becomes its page PageCount_K / PageCount_V
+ *                    when its Q_Buffer_Count_K / Q_Buffer_Count_V is 128; other rows are left alone.
+ * kitty_decode_attn_rows: kitty_decode_attn over the whole sequence of every row. */
+int kitty_append_rows(const kitty_layer *layer, const kitty_counts *row_counts_host, const kitty_counts *row_counts_dev,
+                      const void *key, const void *value, int dtype, int64_t k_stride_b, int64_t k_stride_h,
+                      int64_t v_stride_b, int64_t v_stride_h, int32_t B, void *stream);
+int kitty_flush_rows(const kitty_layer *layer, const kitty_counts *row_counts_host, const kitty_counts *row_counts_dev,
+                     int32_t B, int select, int div_mode, void *stream);
+int kitty_decode_attn_rows(const kitty_layer *layer, const kitty_counts *row_counts_host,
+                           const kitty_counts *row_counts_dev, const void *query, int q_dtype, int32_t B, int32_t h_q,
+                           float scaling, void *out, int out_dtype, void *workspace, int64_t workspace_bytes, int impl,
+                           void *stream);
+
 /* ---- Decode step with device-resident state (CUDA-graph friendly) ------------------------
  * The reference passes its counters to every kernel as Python ints
  * (kernels/kitty_attention.py:458-460, 510-514), which bakes them into a captured graph.  Here the

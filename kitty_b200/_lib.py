@@ -23,7 +23,8 @@ EXPORTS = [
     "kitty_append", "kitty_flush", "kitty_decode_workspace_bytes", "kitty_workspace_status", "kitty_decode_attn",
     "kitty_lse_merge", "kitty_decode_attn_static", "kitty_plan_step", "kitty_decode_step",
     "kitty_lse_exchange_bytes", "kitty_lse_exchange_merge", "kitty_decode_attn_exchange", "kitty_rope_qk",
-    "kitty_plan_step_split", "kitty_decode_step_exchange",
+    "kitty_plan_step_split", "kitty_decode_step_exchange", "kitty_append_rows", "kitty_flush_rows",
+    "kitty_decode_attn_rows",
 ]
 
 
@@ -112,6 +113,13 @@ def lib() -> C.CDLL:
     L.kitty_decode_step_exchange.argtypes = [C.POINTER(KittyLayer), vp, vp, vp, C.c_int, i64, i64, i64, i64, vp, C.c_int,
                                              i32, i32, C.c_float, vp, C.c_int, vp, i64, C.c_int, vp, i32, i32, i32, vp,
                                              i64, vp]
+    L.kitty_append_rows.restype = C.c_int
+    L.kitty_append_rows.argtypes = [C.POINTER(KittyLayer), vp, vp, vp, vp, C.c_int, i64, i64, i64, i64, i32, vp]
+    L.kitty_flush_rows.restype = C.c_int
+    L.kitty_flush_rows.argtypes = [C.POINTER(KittyLayer), vp, vp, i32, C.c_int, C.c_int, vp]
+    L.kitty_decode_attn_rows.restype = C.c_int
+    L.kitty_decode_attn_rows.argtypes = [C.POINTER(KittyLayer), vp, vp, vp, C.c_int, i32, i32, C.c_float, vp, C.c_int,
+                                         vp, i64, C.c_int, vp]
     L.kitty_decode_attn_exchange.restype = C.c_int
     L.kitty_decode_attn_exchange.argtypes = [C.POINTER(KittyLayer), C.POINTER(KittyCounts), vp, C.c_int, i32, i32,
                                              C.c_float, vp, C.c_int, vp, i64, i32, i32, i32, C.c_int, vp, i32, i32, i32,

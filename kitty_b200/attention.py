@@ -42,6 +42,15 @@ def decode_attention(query: torch.Tensor, kv_cache: KVCache_Layer, num_kv_heads:
     else:
         assert partial_out.dtype == torch.float32 and partial_out.is_contiguous()
         assert tuple(partial_out.shape) == (B, H_Q, D + 2)
+    if kv_cache.row_counts is not None:
+        # ragged batch: every row has its own counters (whole sequence of every row; no split over GPUs)
+        assert partial_out is None and exchange is None and (page_begin, page_end, flags) == (0, -1, 3)
+        host, dev = kv_cache.row_ptrs()
+        rc = _lib.lib().kitty_decode_attn_rows(kv_cache.c_layer(), host, dev, query.data_ptr(),
+                                               _lib.dtype_code(query.dtype), B, H_Q, float(scaling), out_ptr, out_code,
+                                               ws.data_ptr(), ws.numel(), impl, _lib.stream_ptr(query.device))
+        _lib.check(rc, "kitty_decode_attn_rows")
+        return out
     layer, counts = kv_cache.c_layer(), kv_cache.c_counts()
     if exchange is not None:
         assert partial_out is None and B * H_Q == exchange.rows

@@ -13,6 +13,7 @@ from __future__ import annotations
 
 from typing import Any, Optional
 
+import numpy as np
 import torch
 from transformers.cache_utils import Cache
 
@@ -61,11 +62,18 @@ class KittyCache(Cache):
         """Prefill (first call of a layer): remember the prompt's K/V and return True.
         Decode: append one token per sequence and return False."""
         lay = self.kv_cache[layer_idx]
-        if lay.Sink_Count == 0:
+        lengths = (cache_kwargs or {}).get("lengths")
+        if lay.Sink_Count == 0 and lay.row_counts is None:
             lay.key_states, lay.value_states = key_states, value_states
+            lay.prompt_lengths = None if lengths is None else [int(x) for x in lengths]
             return True
-        assert key_states.shape[-2] == 1 and value_states.shape[-2] == 1, \
-            "Decode: key_states and value_states should have sequence length of 1."
+        if key_states.shape[-2] != 1 or lengths is not None:
+            # a further piece of the prompt (chunked prefill), possibly of a different length per row
+            self._append_chunk(lay, key_states, value_states, lengths)
+            return False
+        if lay.row_counts is not None:
+            self._append_rows(lay, key_states, value_states, None)
+            return False
         B = key_states.shape[0]
         if key_states.stride(-1) != 1:
             key_states = key_states.contiguous()
@@ -95,6 +103,127 @@ class KittyCache(Cache):
                 lay.Write_Offset_Local_V = (lay.Write_Offset_Local_V + 1) % lay.PAGE_SIZE
         return False
 
+    # -- ragged batches and prompts that arrive in pieces -------------------------------------------- #
+    # The reference detects the prompt by Sink_Count == 0 and keeps one set of counters per layer
+    # (kvcache/kitty.py:89-95, utils_kv_per_layer.py:53-80): all rows the same length, the prompt in one piece.
+    # Here update(..., cache_kwargs={"lengths": [...]}) gives every row its own length (keys / values right-padded
+    # to the longest), and a later update() with more than one token appends a further piece of the prompt.  The
+    # layer then carries one set of counters per row (KVCache_Layer.row_counts) and the *_rows entry points run.
+    @staticmethod
+    def _advance_append(rc: np.ndarray, active: np.ndarray, S: int, P: int) -> None:
+        """Counters after one appended token per active row (kvcache/kitty.py:102-123, row-wise)."""
+        sink_room = active & (rc[:, 2] < S)
+        rest = active & ~sink_room
+        rc[sink_room, 2] += 1
+        rc[rest, 3] += 1
+        ring_room = rest & (rc[:, 5] < P)
+        evict = rest & ~ring_room
+        rc[ring_room, 5] += 1
+        rc[evict, 4] += 1
+        rc[evict, 6] = (rc[evict, 6] + 1) % P
+
+    @staticmethod
+    def _advance_flush(rc: np.ndarray, P: int) -> None:
+        """Counters after the flushes that are due (kvcache/kitty.py:201-234, row-wise)."""
+        fk, fv = rc[:, 3] == P, rc[:, 4] == P
+        rc[fk, 0] += 1
+        rc[fk, 3] = 0
+        rc[fv, 1] += 1
+        rc[fv, 4] = 0
+
+    def _append_rows(self, lay, key_states, value_states, active) -> None:
+        """One token per row (rows where `active` is False take none), per-row counters."""
+        B = key_states.shape[0]
+        if key_states.stride(-1) != 1:
+            key_states = key_states.contiguous()
+        if value_states.stride(-1) != 1:
+            value_states = value_states.contiguous()
+        if value_states.dtype != key_states.dtype:
+            value_states = value_states.to(key_states.dtype)
+        rc = lay.row_counts
+        act = np.ones(lay.MAX_BS, dtype=bool) if active is None else np.asarray(active, dtype=bool).copy()
+        act[B:] = False
+        rc[:, 7] = np.where(act, 0, 1)                       # `reserved` != 0: the kernel skips the row
+        assert (rc[act, 3] < lay.PAGE_SIZE).all() and (rc[act, 4] < lay.PAGE_SIZE).all()
+        lay.sync_rows()
+        host, dev = lay.row_ptrs()
+        rc_ = _lib.lib().kitty_append_rows(lay.c_layer(), host, dev, key_states.data_ptr(), value_states.data_ptr(),
+                                           _lib.dtype_code(key_states.dtype), key_states.stride(0),
+                                           key_states.stride(1), value_states.stride(0), value_states.stride(1), B,
+                                           _lib.stream_ptr(key_states.device))
+        _lib.check(rc_, "kitty_append_rows")
+        self._advance_append(rc, act, lay.S, lay.PAGE_SIZE)
+        rc[:, 7] = 0
+        lay.sync_rows()
+
+    def _flush_rows(self, lay) -> None:
+        rc = lay.row_counts
+        if not ((rc[:, 3] == lay.PAGE_SIZE) | (rc[:, 4] == lay.PAGE_SIZE)).any():
+            return
+        if self.selection != "fused":
+            raise ValueError("per-row counters select channels inside the flush kernel (selection='fused')")
+        host, dev = lay.row_ptrs()
+        rc_ = _lib.lib().kitty_flush_rows(lay.c_layer(), host, dev, lay.MAX_BS, _lib.SELECT_FUSED, self.div_mode,
+                                          _lib.stream_ptr(lay.device))
+        _lib.check(rc_, "kitty_flush_rows")
+        self._advance_flush(rc, lay.PAGE_SIZE)
+        lay.sync_rows()
+        lay.ensure_pages(lay.PageCount_K + 1, lay.PageCount_V + 1)
+
+    def _append_chunk(self, lay, key_states, value_states, lengths) -> None:
+        """A further piece of the prompt: n tokens per row (lengths[b] <= n of them for row b), appended in order.
+        The state afterwards is the one n decode steps would have left: tokens pass through the sink, the Q-buffers
+        and the value ring, and every Q-buffer that fills up becomes a page.  One append (and, when due, one flush)
+        launch per token position."""
+        B, _, n, _ = key_states.shape
+        lens = np.full(lay.MAX_BS, 0, dtype=np.int64)
+        lens[:B] = n if lengths is None else np.asarray([int(x) for x in lengths], dtype=np.int64)
+        assert (lens <= n).all() and (lens >= 0).all()
+        lay.make_ragged()
+        lay.ensure_pages(lay.PageCount_K + 2 + n // lay.PAGE_SIZE, lay.PageCount_V + 2 + n // lay.PAGE_SIZE)
+        for t in range(int(lens.max())):
+            self._append_rows(lay, key_states[:, :, t:t + 1], value_states[:, :, t:t + 1], lens > t)
+            self._flush_rows(lay)
+
+    def _quantize_prefill_ragged(self, lay, k, v) -> None:
+        """Prompt with one length per row: each row is partitioned and quantized as a batch of one (the kernels see a
+        view of the layer that starts at the row)."""
+        B, _, Lmax, _ = k.shape
+        lens = lay.prompt_lengths
+        assert len(lens) == B and all(0 < L <= Lmax for L in lens)
+        P = lay.PAGE_SIZE
+        rc = np.zeros((lay.MAX_BS, 8), dtype=np.int32)
+        lay.ensure_pages((max(lens) - lay.S) // P + 1, (max(lens) - lay.S) // P + 1)
+        for b, L in enumerate(lens):
+            sink = min(lay.S, L)
+            qbuf_k = (L - sink) % P
+            pages_k = (L - sink - qbuf_k) // P
+            local_v = min(P, L - sink)
+            qbuf_v = (L - sink - local_v) % P
+            pages_v = (L - sink - local_v - qbuf_v) // P
+            sub = _lib.KittyLayer.from_buffer_copy(lay.c_layer())
+            sub.max_bs = 1
+            for name in ("Sink_Buffer_K", "Sink_Buffer_V", "Q_Buffer_K", "Q_Buffer_V", "Local_Buffer_V"):
+                setattr(sub, name, getattr(lay, name)[b].data_ptr())
+            kb_, vb_ = k[b:b + 1], v[b:b + 1]
+            rc_ = _lib.lib().kitty_prefill_tails(sub, kb_.data_ptr(), vb_.data_ptr(), _lib.dtype_code(k.dtype),
+                                                 kb_.stride(0), kb_.stride(1), kb_.stride(2), vb_.stride(0),
+                                                 vb_.stride(1), vb_.stride(2), 1, L, sink, qbuf_k, local_v, qbuf_v,
+                                                 _lib.stream_ptr(k.device))
+            _lib.check(rc_, "kitty_prefill_tails")
+            if pages_k > 0:
+                quantize_pack_k(kb_, sink, pages_k, lay.PageTable_K[b:b + 1], 0, lay.KeyCache, lay.KeyCache_metadata, P,
+                                lay.D_BOOSTED, selection=self.selection, div_mode=self.div_mode)
+            if pages_v > 0:
+                quantize_pack_v(vb_, sink, pages_v, lay.PageTable_V[b:b + 1], 0, lay.ValueCache,
+                                lay.ValueCache_metadata, P, div_mode=self.div_mode)
+            rc[b, :7] = (pages_k, pages_v, sink, qbuf_k, qbuf_v, local_v, 0)
+        lay.row_counts = rc
+        lay._row_dev = torch.zeros((lay.MAX_BS, 8), dtype=torch.int32, device=lay.device)
+        lay.sync_rows()
+        lay.prompt_lengths = None
+        lay.key_states = lay.value_states = None
+
     def quantize_prefill(self, layer_idx: int = 0) -> None:
         lay = self.kv_cache[layer_idx]
         if lay.key_states is None or lay.value_states is None:
@@ -106,6 +235,8 @@ class KittyCache(Cache):
             v = v.contiguous()
         if v.dtype != k.dtype:
             v = v.to(k.dtype)
+        if lay.prompt_lengths is not None:
+            return self._quantize_prefill_ragged(lay, k, v)
         B, _, L, _ = k.shape
         P = lay.PAGE_SIZE
         sink = min(lay.S, L)
@@ -138,6 +269,8 @@ class KittyCache(Cache):
     def quantize_decode(self, layer_idx: int = 0) -> None:
         """A Q-buffer that holds a full page becomes the next packed page (keys and values independently)."""
         lay = self.kv_cache[layer_idx]
+        if lay.row_counts is not None:
+            return self._flush_rows(lay)
         fk = lay.Q_Buffer_Count_K == lay.PAGE_SIZE
         fv = lay.Q_Buffer_Count_V == lay.PAGE_SIZE
         if not (fk or fv):
@@ -186,6 +319,9 @@ class KittyCache(Cache):
             raise ValueError("the device-resident decode step selects channels inside the flush kernel "
                              "(selection='fused')")
         lay0 = self.kv_cache[0]
+        if lay0.row_counts is not None:
+            raise ValueError("the device-resident decode step keeps one set of counters for the batch; a ragged batch "
+                             "uses update() / kitty_attention_forward() / quantize_decode()")
         ref = self._counter_tuple(lay0)
         for lay in self.kv_cache[1:]:
             if self._counter_tuple(lay) != ref:

@@ -44,7 +44,15 @@ struct DecodeArgs {
   float *partials;       // [B*H, n_slots, G, PART]
   int32_t *status;       // workspace header: [0] set non-zero when a bounded wait ran out, [1] item hand-out counter
   const kitty_step_state *dyn;   // or null.  Non-null: plan, counters and item counts are read from it on the device
+  const kitty_counts *rows;      // or null.  Non-null: one set of counters per batch row (ragged batch); C and the
+                                 // plan then hold the largest values over the rows, and a row stops where its own
+                                 // counters say
 };
+
+// Counters of batch row b: the row's own when the call carries per-row counters, the call's otherwise.
+__device__ __forceinline__ kitty_counts row_counts(const DecodeArgs &a, const kitty_counts &C, int b) {
+  return a.rows != nullptr ? a.rows[b] : C;
+}
 
 // Merge n partials per row.  Row r's partial s lives at
 //   base + ((r / gm) * ns * gm + r % gm) * PART + s * stride_part   (floats).

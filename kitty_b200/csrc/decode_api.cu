@@ -101,11 +101,27 @@ extern "C" int64_t kitty_decode_workspace_bytes(int32_t B, int32_t h_kv, int32_t
   return WS_HEADER + (chunk_slots + bh * EDGE_PARTS_MAX) * G * PART * static_cast<int64_t>(sizeof(float));
 }
 
+static bool counts_ok(const kitty_layer *layer, const kitty_counts &C) {
+  if (C.PageCount_K < 0 || C.PageCount_V < 0 || C.PageCount_K > layer->max_page || C.PageCount_V > layer->max_page ||
+      C.Sink_Count < 0 || C.Sink_Count > SINK || C.Q_Buffer_Count_K < 0 || C.Q_Buffer_Count_K > PAGE ||
+      C.Q_Buffer_Count_V < 0 || C.Q_Buffer_Count_V > PAGE || C.Local_Count_V < 0 || C.Local_Count_V > PAGE ||
+      C.Write_Offset_Local_V < 0 || C.Write_Offset_Local_V >= PAGE)
+    return false;
+  const int64_t tk = static_cast<int64_t>(C.PageCount_K) * PAGE + C.Q_Buffer_Count_K;
+  const int64_t tv = static_cast<int64_t>(C.PageCount_V) * PAGE + C.Q_Buffer_Count_V + C.Local_Count_V;
+  return tk == tv && C.PageCount_V <= C.PageCount_K && !(C.Sink_Count < SINK && tk != 0);
+}
+
+// rows_host / rows_dev: null, or one set of counters per batch row (ragged batch; host copy for the checks and the
+// plan, device copy for the kernels).  `counts` is then ignored: the plan is made for the largest values over the rows
+// and every row stops where its own counters say.
 static int decode_attn_core(const kitty_layer *layer, const kitty_counts *counts, const void *query, int q_dtype,
                             int32_t B, int32_t h_q, float scaling, void *out, int out_dtype, void *workspace,
                             int64_t workspace_bytes, int32_t page_begin, int32_t page_end, int32_t flags,
-                            float *partial_out, int impl, const XchgDesc *xchg, void *stream) {
-  if (!layer || !counts || !query || !workspace) return KITTY_E_BADARG;
+                            float *partial_out, int impl, const XchgDesc *xchg, void *stream,
+                            const kitty_counts *rows_host = nullptr, const kitty_counts *rows_dev = nullptr) {
+  if (!layer || (!counts && !rows_host) || !query || !workspace) return KITTY_E_BADARG;
+  if ((rows_host != nullptr) != (rows_dev != nullptr)) return KITTY_E_BADARG;
   if (!out && !partial_out) return KITTY_E_BADARG;
   if (layer->head_dim != HD || layer->page_size != PAGE || layer->d_boost != DB || layer->sink_size != SINK)
     return KITTY_E_BADSHAPE;
@@ -116,16 +132,30 @@ static int decode_attn_core(const kitty_layer *layer, const kitty_counts *counts
   if (q_dtype < KITTY_F16 || q_dtype > KITTY_F32 || out_dtype < KITTY_F16 || out_dtype > KITTY_F32) return KITTY_E_BADARG;
   if (impl < 0 || impl > 2) return KITTY_E_BADARG;
   if (B > 65535 || H > 65535) return KITTY_E_BADARG;
-  const kitty_counts &C = *counts;
-  if (C.PageCount_K < 0 || C.PageCount_V < 0 || C.PageCount_K > layer->max_page || C.PageCount_V > layer->max_page ||
-      C.Sink_Count < 0 || C.Sink_Count > SINK || C.Q_Buffer_Count_K < 0 || C.Q_Buffer_Count_K > PAGE ||
-      C.Q_Buffer_Count_V < 0 || C.Q_Buffer_Count_V > PAGE || C.Local_Count_V < 0 || C.Local_Count_V > PAGE ||
-      C.Write_Offset_Local_V < 0 || C.Write_Offset_Local_V >= PAGE)
-    return KITTY_E_BADARG;
-  const int64_t tk = static_cast<int64_t>(C.PageCount_K) * PAGE + C.Q_Buffer_Count_K;
-  const int64_t tv = static_cast<int64_t>(C.PageCount_V) * PAGE + C.Q_Buffer_Count_V + C.Local_Count_V;
-  if (tk != tv || C.PageCount_V > C.PageCount_K) return KITTY_E_BADARG;          // utils_kv_per_layer.py:94
-  if (C.Sink_Count < SINK && tk != 0) return KITTY_E_BADARG;                      // pages exist only once the sink is full
+  // C: the counters the plan is made for.  Uniform batch: the call's.  Ragged batch: a stand-in holding the largest
+  // number of common pages, the longest sink and the longest tail over the rows.
+  kitty_counts C;
+  int64_t tk;
+  if (rows_host == nullptr) {
+    C = *counts;
+    if (!counts_ok(layer, C)) return KITTY_E_BADARG;              // includes utils_kv_per_layer.py:94 (K and V lengths agree)
+    tk = static_cast<int64_t>(C.PageCount_K) * PAGE + C.Q_Buffer_Count_K;
+  } else {
+    int pv = 0, sink = 0, tail = 0;
+    for (int b = 0; b < B; ++b) {
+      const kitty_counts &r = rows_host[b];
+      if (!counts_ok(layer, r)) return KITTY_E_BADARG;
+      pv = std::max(pv, r.PageCount_V);
+      sink = std::max(sink, r.Sink_Count);
+      tail = std::max(tail, (r.PageCount_K - r.PageCount_V) * PAGE + r.Q_Buffer_Count_K);
+    }
+    C = kitty_counts{};
+    C.PageCount_V = pv;
+    C.PageCount_K = pv + tail / PAGE;
+    C.Q_Buffer_Count_K = tail % PAGE;
+    C.Sink_Count = sink;
+    tk = static_cast<int64_t>(C.PageCount_K) * PAGE + C.Q_Buffer_Count_K;
+  }
   if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return KITTY_E_BADARG;
 
   DecodeArgs a;
@@ -167,6 +197,7 @@ static int decode_attn_core(const kitty_layer *layer, const kitty_counts *counts
   a.scale_log2 = scaling * 1.4426950408889634f;
   a.status = static_cast<int32_t *>(workspace);
   a.dyn = nullptr;
+  a.rows = rows_dev;
   a.partials = reinterpret_cast<float *>(static_cast<uint8_t *>(workspace) + WS_HEADER);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
@@ -223,6 +254,15 @@ extern "C" int kitty_decode_attn(const kitty_layer *layer, const kitty_counts *c
                           page_begin, page_end, flags, partial_out, impl, nullptr, stream);
 }
 
+extern "C" int kitty_decode_attn_rows(const kitty_layer *layer, const kitty_counts *row_counts_host,
+                                      const kitty_counts *row_counts_dev, const void *query, int q_dtype, int32_t B,
+                                      int32_t h_q, float scaling, void *out, int out_dtype, void *workspace,
+                                      int64_t workspace_bytes, int impl, void *stream) {
+  if (!row_counts_host || !row_counts_dev || !out) return KITTY_E_BADARG;
+  return decode_attn_core(layer, nullptr, query, q_dtype, B, h_q, scaling, out, out_dtype, workspace, workspace_bytes, 0, -1,
+                          3, nullptr, impl, nullptr, stream, row_counts_host, row_counts_dev);
+}
+
 extern "C" int kitty_decode_attn_exchange(const kitty_layer *layer, const kitty_counts *counts, const void *query,
                                           int q_dtype, int32_t B, int32_t h_q, float scaling, void *out, int out_dtype,
                                           void *workspace, int64_t workspace_bytes, int32_t page_begin, int32_t page_end,
@@ -268,17 +308,6 @@ extern "C" int kitty_lse_merge(const float *partials, int32_t n_parts, int64_t r
 // ------------------------------------------------------------------------- //
 // Decode step with device-resident state
 // ------------------------------------------------------------------------- //
-static bool counts_ok(const kitty_layer *layer, const kitty_counts &C) {
-  if (C.PageCount_K < 0 || C.PageCount_V < 0 || C.PageCount_K > layer->max_page || C.PageCount_V > layer->max_page ||
-      C.Sink_Count < 0 || C.Sink_Count > SINK || C.Q_Buffer_Count_K < 0 || C.Q_Buffer_Count_K > PAGE ||
-      C.Q_Buffer_Count_V < 0 || C.Q_Buffer_Count_V > PAGE || C.Local_Count_V < 0 || C.Local_Count_V > PAGE ||
-      C.Write_Offset_Local_V < 0 || C.Write_Offset_Local_V >= PAGE)
-    return false;
-  const int64_t tk = static_cast<int64_t>(C.PageCount_K) * PAGE + C.Q_Buffer_Count_K;
-  const int64_t tv = static_cast<int64_t>(C.PageCount_V) * PAGE + C.Q_Buffer_Count_V + C.Local_Count_V;
-  return tk == tv && C.PageCount_V <= C.PageCount_K && !(C.Sink_Count < SINK && tk != 0);
-}
-
 __global__ void store_step_state_kernel(kitty_step_state st, kitty_step_state *dst) {
   const int32_t *src = reinterpret_cast<const int32_t *>(&st);
   const int n = static_cast<int>(sizeof(kitty_step_state) / sizeof(int32_t));
@@ -397,6 +426,7 @@ static int decode_step_core(const kitty_layer *layer, const kitty_step_state *de
   a.status = static_cast<int32_t *>(workspace);
   a.partials = reinterpret_cast<float *>(static_cast<uint8_t *>(workspace) + WS_HEADER);
   a.dyn = device_state;
+  a.rows = nullptr;
   // fixed grids: the item counts are read on the device
   if (G <= 8) {
     if (int rc = launch_decode_paged_i8(a, 0, 0, i8_blocks_per_sm(G) * sm_count(), s, true)) return rc;

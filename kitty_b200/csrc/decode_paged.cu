@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(PG_WARPS * 32) decode_paged_kernel(DecodeArgs 
     const int bh = item / (P.nchunk * n_gt);
     const int h = bh % H, b = bh / H;
     const int p0 = P.pb + c * P.ch;
-    const int p1 = min(P.pe, p0 + P.ch);
+    const int p1 = min(a.rows != nullptr ? min(P.pe, a.rows[b].PageCount_V) : P.pe, p0 + P.ch);
     const int g_valid = min(8, G - gt * 8);
 
     __syncthreads();   // previous item's merge buffer (overlaying the stages) and query are no longer read
@@ -317,7 +317,7 @@ __global__ void __launch_bounds__(PG_WARPS * 32) decode_paged_kernel(DecodeArgs 
   for (int e = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x); e < n_edge; e += gridDim.x) {
     __syncthreads();     // the previous item's merge buffer / edge buffers are no longer read
     const int ebh = e / P.edge_parts, part = e % P.edge_parts;
-    edge_item<NGE, PG_WARPS>(a, P, C, es, ebh / H, ebh % H, part);
+    edge_item<NGE, PG_WARPS>(a, P, row_counts(a, C, ebh / H), es, ebh / H, ebh % H, part);
   }
 }
 

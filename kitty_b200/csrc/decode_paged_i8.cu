@@ -240,7 +240,8 @@ __global__ void __launch_bounds__(I8_WARPS * 32, NG == 1 ? 4 : 3) decode_paged_i
     if (e_after > e_before) {
       // ---- edge item: one part of the sink + tail of one (batch, kv-head), by the whole block ---- //
       const int ebh = e_before / P.edge_parts, part = e_before % P.edge_parts;
-      edge_item<4 * NG, I8_WARPS>(a, P, C, smem.u.e, ebh / H, ebh % H, part, smem_u32(&smem.bar_e), &edge_phase);
+      edge_item<4 * NG, I8_WARPS>(a, P, row_counts(a, C, ebh / H), smem.u.e, ebh / H, ebh % H, part,
+                                  smem_u32(&smem.bar_e), &edge_phase);
       __syncthreads();
       ws.inv[lane] = 0;  // the slot table was overwritten: keep its entries valid positions
       if (tid == 0) smem.next_item = it_next;
@@ -251,7 +252,7 @@ __global__ void __launch_bounds__(I8_WARPS * 32, NG == 1 ? 4 : 3) decode_paged_i
     const int bh = item / P.nchunk;
     const int h = bh % H, b = bh / H;
     const int p0 = P.pb + c * P.ch;
-    const int p1 = min(P.pe, p0 + P.ch);
+    const int p1 = min(a.rows != nullptr ? min(P.pe, a.rows[b].PageCount_V) : P.pe, p0 + P.ch);
 
     // this warp's pages: p0 + warp, p0 + warp + I8_WARPS, ...  (requested first: the copies fly while the
     // query is staged)

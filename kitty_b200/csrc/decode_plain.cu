@@ -29,9 +29,9 @@ __global__ void __launch_bounds__(128) decode_plain_kernel(DecodeArgs a) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   PlainSmem &sm = *reinterpret_cast<PlainSmem *>(smem_raw);
   const DecodePlan &P = a.P;
-  const kitty_counts &C = a.C;
   const int tid = threadIdx.x;
   const int h = blockIdx.y, b = blockIdx.z, H = P.H, G = P.G;
+  const kitty_counts C = row_counts(a, a.C, b);
   const int64_t bh = static_cast<int64_t>(b) * H + h;
 
   // ---- which tiles, which slot ---- //
@@ -44,10 +44,13 @@ __global__ void __launch_bounds__(128) decode_plain_kernel(DecodeArgs a) {
       j -= P.has_sink;
       if (!P.fast_chunks && j < P.nchunk) {
         const int p0 = P.pb + j * P.ch;
-        const int p1 = min(P.pe, p0 + P.ch);
+        const int p1 = max(p0, min(min(P.pe, C.PageCount_V), p0 + P.ch));
         u0 = 1 + p0; u1 = 1 + p1; slot = P.has_sink + j;
       } else {
-        u0 = C.PageCount_V + 1; u1 = P.n_tiles; slot = P.has_sink + P.nchunk;
+        // the tail of this row: its own number of tiles (P.n_tiles is the largest over the rows)
+        u0 = C.PageCount_V + 1;
+        u1 = 1 + (C.PageCount_K * PAGE + C.Q_Buffer_Count_K + PAGE - 1) / PAGE;
+        slot = P.has_sink + P.nchunk;
       }
     }
   }

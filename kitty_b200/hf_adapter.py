@@ -116,7 +116,8 @@ def _fused_step_ok(cache, layer_idx: int, q, k, v) -> bool:
         return False
     if layer_idx == 0:
         lay0 = cache.kv_cache[0]
-        return lay0.Sink_Count > 0 and q.shape[1] // lay0.H_KV <= 16     # layer 0 always starts a new step
+        # layer 0 always starts a new step; a ragged batch (per-row counters) takes the three-call path
+        return lay0.Sink_Count > 0 and lay0.row_counts is None and q.shape[1] // lay0.H_KV <= 16
     return cache._step_host is not None           # a step planned at layer 0 is under way
 
 

@@ -12,6 +12,7 @@ from __future__ import annotations
 import math
 from typing import Optional
 
+import numpy as np
 import torch
 
 from . import _lib
@@ -101,6 +102,13 @@ class KVCache_Layer:
         self.Write_Offset_Local_V = 0
         self.key_states: Optional[torch.Tensor] = None
         self.value_states: Optional[torch.Tensor] = None
+        # Ragged batches.  The reference keeps one set of counters for the whole batch (the ints above,
+        # utils_kv_per_layer.py:53-80).  When the rows of a batch differ in length, `row_counts` holds one set per
+        # row — int32 [MAX_BS, 8] in the field order of struct kitty_counts — with a device mirror for the kernels,
+        # and the ints above hold the largest value over the rows.
+        self.row_counts: Optional[np.ndarray] = None
+        self._row_dev: Optional[torch.Tensor] = None
+        self.prompt_lengths = None        # lengths given with a ragged prompt, until quantize_prefill() consumes them
         self._c_layer = None
         self._c_counts = None
         # scratch of the decode kernels, in a one-element box so that the layers of a cache can share one buffer
@@ -110,10 +118,44 @@ class KVCache_Layer:
 
     # -- reference surface ------------------------------------------------- #
     def get_total_length(self) -> int:
+        if self.row_counts is not None:           # ragged: the longest row
+            return int(self.row_lengths().max())
         seqlen_k = self.PageCount_K * self.PAGE_SIZE + self.Sink_Count + self.Q_Buffer_Count_K
         seqlen_v = self.PageCount_V * self.PAGE_SIZE + self.Sink_Count + self.Q_Buffer_Count_V + self.Local_Count_V
         assert seqlen_k == seqlen_v, f"seqlen_K: {seqlen_k}, seqlen_V: {seqlen_v}"
         return seqlen_k
+
+    # -- per-row counters (ragged batches) -------------------------------------- #
+    ROW_FIELDS = ("PageCount_K", "PageCount_V", "Sink_Count", "Q_Buffer_Count_K", "Q_Buffer_Count_V", "Local_Count_V",
+                  "Write_Offset_Local_V")
+
+    def make_ragged(self) -> None:
+        """Switch to per-row counters, every row starting from the shared ones."""
+        if self.row_counts is None:
+            rc = np.zeros((self.MAX_BS, 8), dtype=np.int32)
+            for i, name in enumerate(self.ROW_FIELDS):
+                rc[:, i] = getattr(self, name)
+            self.row_counts = rc
+            self._row_dev = torch.zeros((self.MAX_BS, 8), dtype=torch.int32, device=self.device)
+            self.sync_rows()
+
+    def row_lengths(self) -> np.ndarray:
+        rc = self.row_counts
+        k = rc[:, 0] * self.PAGE_SIZE + rc[:, 2] + rc[:, 3]
+        v = rc[:, 1] * self.PAGE_SIZE + rc[:, 2] + rc[:, 4] + rc[:, 5]
+        assert (k == v).all(), f"seqlen_K: {k}, seqlen_V: {v}"
+        return k
+
+    def sync_rows(self) -> None:
+        """Copy the per-row counters to the device mirror (in stream order: a kernel launched afterwards sees them,
+        one launched before does not) and refresh the shared ints with the largest value over the rows."""
+        self._row_dev.copy_(torch.from_numpy(self.row_counts.copy()))
+        for i, name in enumerate(self.ROW_FIELDS):
+            setattr(self, name, int(self.row_counts[:, i].max()))
+
+    def row_ptrs(self):
+        """(host pointer, device pointer) of the per-row counters for the C entry points."""
+        return self.row_counts.ctypes.data, self._row_dev.data_ptr()
 
     # -- pooled page rows ----------------------------------------------------- #
     def ensure_pages(self, pages_k: int, pages_v: int) -> None:
@@ -145,6 +187,7 @@ class KVCache_Layer:
         self.Sink_Count = self.Q_Buffer_Count_K = self.Q_Buffer_Count_V = 0
         self.Local_Count_V = self.Write_Offset_Local_V = 0
         self.key_states = self.value_states = None
+        self.row_counts = self._row_dev = self.prompt_lengths = None
 
     # -- C-ABI views --------------------------------------------------------- #
     def c_layer(self) -> "_lib.KittyLayer":

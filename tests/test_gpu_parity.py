@@ -302,7 +302,8 @@ def test_argument_errors(kb):
     rc = _lib.lib().kitty_decode_attn(lay.c_layer(), bad, q.data_ptr(), 0, 1, 8, 1.0, q.data_ptr(), 0,
                                       lay.workspace(1, 8).data_ptr(), lay.workspace(1, 8).numel(), 0, -1, 3, None, 0, None)
     assert rc == _lib.KITTY_E_BADARG
-    with pytest.raises(AssertionError):             # a second multi-token update is not a decode step
+    with pytest.raises(_lib.KittyError):            # further pieces of the prompt until the cache's 4 pages are full
+        cache.update(k.to(DEV), v.to(DEV), 0)
         cache.update(k.to(DEV), v.to(DEV), 0)
 
 

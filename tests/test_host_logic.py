@@ -3,6 +3,7 @@ for the CUDA library: the counters must follow the oracle's (i.e. the
 reference's) transitions and the right entry points must be called."""
 import types
 
+import numpy as np
 import pytest
 import torch
 
@@ -23,12 +24,18 @@ class FakeLayer:
             setattr(self, c, 0)
         self.key_states = self.value_states = None
         self._ws_box = [None]
+        self.row_counts = self.prompt_lengths = None
         for n in ("PageTable_K", "PageTable_V", "KeyCache", "KeyCache_metadata", "ValueCache", "ValueCache_metadata",
                   "Q_Buffer_K", "Q_Buffer_V"):
             setattr(self, n, None)
 
     def c_layer(self):
         return None
+
+    # the per-row counter helpers are plain host code: borrow them from the real layer class
+    from kitty_b200.layer_state import KVCache_Layer as _Real
+    ROW_FIELDS = _Real.ROW_FIELDS
+    make_ragged, row_lengths, sync_rows, row_ptrs = _Real.make_ragged, _Real.row_lengths, _Real.sync_rows, _Real.row_ptrs
 
     def ensure_pages(self, pages_k, pages_v):
         self.ensured.append((pages_k, pages_v))
@@ -102,20 +109,38 @@ def test_counters_follow_the_reference_state_machine(fake, L):
     assert k_flushed == final.PageCount_K - p["pages_k"] and v_flushed == final.PageCount_V - p["pages_v"]
 
 
-def test_update_rejects_multi_token_decode(fake):
-    cache_mod, _ = fake
+def test_a_further_piece_of_the_prompt_is_appended_token_by_token(fake):
+    """A second multi-token update() is a further piece of the prompt: the layer switches to per-row counters, one
+    kitty_append_rows per token position (rows that have run out of tokens are marked inactive), kitty_flush_rows
+    when a Q-buffer is full — and the counters of every row equal the oracle's after the same number of tokens."""
+    cache_mod, calls = fake
     cfg = types.SimpleNamespace(num_hidden_layers=1, head_dim=128, num_key_value_heads=1, num_attention_heads=4,
                                 hidden_size=512)
-    cache = cache_mod.KittyCache(cfg, 1, 512)
-    k = torch.zeros(1, 1, 40, 128, dtype=torch.float16)
-    cache.update(k, k, 0)
+    cache = cache_mod.KittyCache(cfg, 2, 1024)
+    k = torch.zeros(2, 1, 40, 128, dtype=torch.float16)
+    assert cache.update(k, k, 0) is True
     cache.quantize_prefill(0)
-    with pytest.raises(AssertionError):
-        cache.update(k, k, 0)
+    calls.clear()
+    chunk = torch.zeros(2, 1, 300, 128, dtype=torch.float16)
+    assert cache.update(chunk, chunk, 0, {"lengths": [300, 130]}) is False
+    names = [n for n, _ in calls]
+    assert names.count("kitty_append_rows") == 300
+    assert names.count("kitty_flush_rows") == 2          # token 120: a key page of both rows; token 248: row 0's second
+                                                         # key page and first value page, in one launch
+    lay = cache.kv_cache[0]
+    for b, n in enumerate((300, 130)):
+        oc = ko.OracleKittyCache(1, 1, 128, 1, 1024)
+        oc.update(np.zeros((1, 1, 40, 128), np.float32), np.zeros((1, 1, 40, 128), np.float32), 0)
+        oc.quantize_prefill(0)
+        for _ in range(n):
+            oc.update(np.zeros((1, 1, 1, 128), np.float32), np.zeros((1, 1, 1, 128), np.float32), 0)
+            oc.quantize_decode(0)
+        assert [int(x) for x in lay.row_counts[b, :7]] == [getattr(oc.kv_cache[0], c) for c in COUNTERS]
+    assert cache.get_seq_length(0) == 340
     with pytest.raises(ValueError):
         cache.quantize_prefill(0)
-    assert cache.get_mask_sizes(torch.arange(1), 0) == (41, 0)
-    assert len(cache) == 1 and cache.get_max_cache_shape() == 512
+    assert cache.get_mask_sizes(torch.arange(1), 0) == (341, 0)
+    assert len(cache) == 2 - 1 and cache.get_max_cache_shape() == 1024
 
 
 def test_page_pool_hands_out_and_takes_back():
