@@ -224,16 +224,19 @@ __global__ void __launch_bounds__(I8_WARPS * 32, NG == 1 ? 4 : 3) decode_paged_i
   uint32_t inflight = 0;     // bit 0: a key-part copy is in flight, bit 1: a value-part copy (warp-uniform)
   const uint32_t bar_k = smem_u32(&smem.bar_k[warp]), bar_v = smem_u32(&smem.bar_v[warp]), stage_u32 = smem_u32(&ws.stage[0]);
 
-  // Items: a block's first item is its own index; further items are handed out by a work counter in the workspace
-  // header (zero on entry, reset by the merge kernel that always follows), so blocks stay busy until the list is
-  // empty.  The counter is bumped at the START of an item and its result picked up at the end, which hides the
-  // round trip of the atomic.  Edge items are spread evenly through the sequence (position i holds an edge item
-  // when floor((i+1)*n_edge/total) > floor(i*n_edge/total)): at any time most blocks stream pages while a few
-  // reduce a latency-bound edge.
+  // Items are handed out dynamically (a work counter in the workspace header, zero on entry and reset by
+  // the merge kernel that always follows), so blocks stay busy until the list is empty.  (Requesting the next
+  // item ahead of time, to hide the atomic's round trip, measured slower: blocks then hold work they cannot start.)
+  // Edge items are spread evenly through the sequence (position i holds an edge item when
+  // floor((i+1)*n_edge/total) > floor(i*n_edge/total)): at any time most blocks stream pages while a few reduce a
+  // latency-bound edge.
   const long long total = static_cast<long long>(n_items) + n_edge;
-  for (long long it = blockIdx.x; it < total; it = smem.next_item) {
-    int it_next = 0;
-    if (tid == 0) it_next = atomicAdd(a.status + 1, 1) + static_cast<int>(gridDim.x);
+  for (;;) {
+    __syncthreads();     // the previous item's merge buffer, query and work index are no longer read
+    if (tid == 0) smem.next_item = atomicAdd(a.status + 1, 1);
+    __syncthreads();
+    const long long it = smem.next_item;
+    if (it >= total) break;
     const int e_before = static_cast<int>(it * n_edge / total);
     const int e_after = static_cast<int>((it + 1) * n_edge / total);
     const int item = static_cast<int>(it) - e_before;        // index among the page-pair items
@@ -244,8 +247,6 @@ __global__ void __launch_bounds__(I8_WARPS * 32, NG == 1 ? 4 : 3) decode_paged_i
                                   smem_u32(&smem.bar_e), &edge_phase);
       __syncthreads();
       ws.inv[lane] = 0;  // the slot table was overwritten: keep its entries valid positions
-      if (tid == 0) smem.next_item = it_next;
-      __syncthreads();   // the edge buffers are no longer read; the next item's index is visible
       continue;
     }
     const int c = item % P.nchunk;
@@ -594,8 +595,6 @@ __global__ void __launch_bounds__(I8_WARPS * 32, NG == 1 ? 4 : 3) decode_paged_i
         }
       }
     }
-    if (tid == 0) smem.next_item = it_next;
-    __syncthreads();     // the merge buffer and the query are no longer read; the next item's index is visible
   }
 }
 
