@@ -19,8 +19,10 @@ host tensors with the result copied back every step (median of 5 repeats of the
 K steps).  The same line carries one short record for each of the other
 workloads, each with its own CUDA-event timing and byte count: `sweep`
 (attention call at batch 1 / 8 / 32), `quantize` (bulk prefill quantize/pack),
-`model_e2e` (decoder model, greedy decode) on one GPU, and `seqsplit` (the
-131072-token sequence split over the ranks) when launched on more than one.
+`model_e2e` (decoder model, greedy decode) and `reference_gpu` (the reference's
+own Triton kernels on the same GPU, when their copy under baseline/_ref exists)
+on one GPU, and `seqsplit` (the 131072-token sequence split over the ranks) when
+launched on more than one.
 """
 from __future__ import annotations
 
@@ -192,7 +194,7 @@ def cpu_reference(ctx: int, steps: int, warmup: int, budget_s: float = 25.0):
 
 
 # --------------------------------------------------------------------------- #
-def build_cache(kb, batch, ctx, extra, device, seed):
+def build_cache(kb, batch, ctx, extra, device, seed, dtype=torch.bfloat16):
     cfg = argparse.Namespace(num_hidden_layers=1, head_dim=D, num_key_value_heads=H_KV, num_attention_heads=H_Q,
                              hidden_size=H_Q * D)
     cache = kb.KittyCache(cfg, batch, ctx + extra + 256, device=device)
@@ -207,13 +209,13 @@ def build_cache(kb, batch, ctx, extra, device, seed):
         k = torch.randn(b1 - b0, H_KV, ctx, D, generator=g, device=device, dtype=torch.float32)
         for h in range(H_KV):
             k[:, h, :, torch.randperm(D, generator=g, device=device)[:4]] *= 8.0
-        k = k.to(torch.bfloat16)
-        v = torch.randn(b1 - b0, H_KV, ctx, D, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+        k = k.to(dtype)
+        v = torch.randn(b1 - b0, H_KV, ctx, D, generator=g, device=device, dtype=torch.float32).to(dtype)
         sub = _lib.KittyLayer.from_buffer_copy(lay.c_layer())
         for name, rows in (("Sink_Buffer_K", 32), ("Sink_Buffer_V", 32), ("Q_Buffer_K", 128), ("Q_Buffer_V", 128),
                            ("Local_Buffer_V", 128)):
             setattr(sub, name, getattr(lay, name)[b0].data_ptr())
-        rc = _lib.lib().kitty_prefill_tails(sub, k.data_ptr(), v.data_ptr(), _lib.KITTY_BF16, k.stride(0), k.stride(1),
+        rc = _lib.lib().kitty_prefill_tails(sub, k.data_ptr(), v.data_ptr(), _lib.dtype_code(dtype), k.stride(0), k.stride(1),
                                             k.stride(2), v.stride(0), v.stride(1), v.stride(2), b1 - b0, ctx, p["sink"],
                                             p["qbuf_k"], p["local_v"], p["qbuf_v"], _lib.stream_ptr(k.device))
         _lib.check(rc, "kitty_prefill_tails")
@@ -408,6 +410,95 @@ def sweep_record(kb, device, ctx: int, batches=(1, 8, 32)) -> dict:
         del c2
     sweep["how"] = "median of 30 calls, CUDA events around the call, a 256 MB buffer written before each (L2 flushed)"
     return sweep
+
+
+def reference_gpu_record(kb, device, ctx: int, batches=(8, 32)) -> dict:
+    """The reference's own GPU path on this GPU: its Triton kernels from the copy under baseline/_ref (written by
+    oracle/make_ref_copy.py: the slot index widened to int32, nothing else changed), fp16 as the reference requires.
+    Attention: kitty_attention_forward of the reference on the very layer object the CUDA library uses (same field
+    names, shapes and dtypes), next to the library's call — output difference and time of both, L2 flushed before
+    every call.  Quantize: the reference's quantize_pack_k / quantize_pack_v (host prologue included) on one layer
+    call of the bulk workload, next to the library's."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "kitty")):
+        return {"unavailable": "baseline/_ref/kitty is absent (python oracle/make_ref_copy.py <reference checkout> writes it)"}
+    if ref_dir not in sys.path:
+        sys.path.insert(0, ref_dir)
+    try:
+        import kitty.kvcache.kernels.kitty_attention as ra
+        import kitty.kvcache.kernels.kitty_quant_pack as rq
+    except Exception as e:           # noqa: BLE001 - whatever the import raises is the record
+        return {"unavailable": f"import failed: {type(e).__name__}: {str(e).splitlines()[0][:200]}"}
+    mod = argparse.Namespace(num_attention_heads=H_Q, num_key_value_heads=H_KV)
+    scaling = D ** -0.5
+    rec = {"how": "reference = its Triton kernels compiled by the installed Triton for this GPU; fp16 q/k/v; median of "
+                  "20 calls, CUDA events, a 256 MB buffer written before each call (L2 flushed)"}
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+
+    def timed(fn, n=20):
+        for _ in range(3):
+            fn()
+        a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ts = []
+        for _ in range(n):
+            flush_buf.zero_()
+            a.record()
+            fn()
+            z.record()
+            z.synchronize()
+            ts.append(a.elapsed_time(z))
+        return statistics.median(ts) * 1e3
+
+    try:
+        att = {}
+        for b in batches:
+            c2 = build_cache(kb, b, ctx, 64, device, seed=7, dtype=torch.float16)
+            l2 = c2.kv_cache[0]
+            c2.update(torch.randn(b, H_KV, 1, D, device=device).half(), torch.randn(b, H_KV, 1, D, device=device).half(), 0)
+            q = torch.randn(b, H_Q, 1, D, device=device).half()
+            out_ref, _ = ra.kitty_attention_forward(mod, q, l2, scaling)
+            out, _ = kb.kitty_attention_forward(mod, q, l2, scaling)
+            err = float((out.float() - out_ref.float()).abs().max() / out_ref.float().abs().max())
+            us_ref = timed(lambda: ra.kitty_attention_forward(mod, q, l2, scaling))
+            us = timed(lambda: kb.kitty_attention_forward(mod, q, l2, scaling))
+            att[f"batch{b}"] = {"reference_us": us_ref, "ours_us": us, "speedup": us_ref / us, "max_rel_diff": err}
+            del c2
+        rec["attention_32k"] = att
+        # one layer call of the bulk quantize workload, fp16
+        T, pages = 65536, 512
+        g = torch.Generator(device=device).manual_seed(5)
+        sc = torch.exp(torch.rand(1, H_KV, 1, D, generator=g, device=device) * 2.772588722239781)
+        k = (torch.randn(1, H_KV, T, D, generator=g, device=device) * sc).half()
+        v = torch.randn(1, H_KV, T, D, generator=g, device=device).half()
+        z = dict(device=device)
+        bufs = [(torch.zeros(pages, H_KV * 5248, dtype=torch.uint8, **z), torch.zeros(pages, H_KV, 128, 2, dtype=torch.float16, **z),
+                 torch.zeros(pages, H_KV * 4096, dtype=torch.uint8, **z), torch.zeros(pages, H_KV, 128, 2, dtype=torch.float16, **z))
+                for _ in range(2)]
+        pt = torch.arange(pages, dtype=torch.int64, **z).view(1, pages)
+        (rkc, rkm, rvc, rvm), (kc, km, vc, vm) = bufs
+        from kitty_b200 import _lib
+
+        rq.quantize_pack_k(k, 0, pages, pt, 0, rkc, rkm, 128, 32)
+        rq.quantize_pack_v(v, 0, pages, pt, 0, rvc, rvm, 128)
+        kb.quantize_pack_k(k, 0, pages, pt, 0, kc, km, 128, 32, selection="torch", div_mode=_lib.DIV_FULL)
+        kb.quantize_pack_v(v, 0, pages, pt, 0, vc, vm, 128, div_mode=_lib.DIV_FULL)
+        units = pages * H_KV
+        rk = timed(lambda: rq.quantize_pack_k(k, 0, pages, pt, 0, rkc, rkm, 128, 32), 10)
+        rv = timed(lambda: rq.quantize_pack_v(v, 0, pages, pt, 0, rvc, rvm, 128), 10)
+        ok_ = timed(lambda: kb.quantize_pack_k(k, 0, pages, pt, 0, kc, km, 128, 32), 10)
+        ov = timed(lambda: kb.quantize_pack_v(v, 0, pages, pt, 0, vc, vm, 128), 10)
+        rec["quantize_layer_call"] = {
+            "reference_k_us": rk, "ours_k_us": ok_, "k_speedup": rk / ok_, "reference_k_GBps": units * 38528 / rk / 1e3,
+            "reference_v_us": rv, "ours_v_us": ov, "v_speedup": rv / ov, "reference_v_GBps": units * 37376 / rv / 1e3,
+            "same_bytes_with_reference_division_and_selection": {
+                "key_bytes": float((rkc == kc).float().mean()), "key_metadata": float((rkm == km).float().mean()),
+                "value_bytes": float((rvc == vc).float().mean()), "value_metadata": float((rvm == vm).float().mean())},
+            "note": "byte comparison: library run with the index bytes of abs().mean().topk() on this GPU and with "
+                    "div.full.f32, the division Triton compiles; timing: library in its default mode (in-kernel "
+                    "selection, IEEE division)"}
+    except Exception as e:           # noqa: BLE001 - e.g. the Triton build for this GPU failed: record why
+        rec["unavailable"] = f"{type(e).__name__}: {str(e).splitlines()[0][:300]}"
+    return rec
 
 
 def seqsplit_measure(kb, device, rank, world, dist, steps, warmup, seq_batch, exchange, tail_weight):
@@ -715,6 +806,7 @@ def main():
             extras["quantize"] = quantize_record(device)
             torch.cuda.empty_cache()
             extras["model_e2e"] = model_record(device)
+            extras["reference_gpu"] = reference_gpu_record(kb, device, args.ctx)
         else:
             extras["seqsplit"] = seqsplit_record(kb, device, rank, world, dist)
 
