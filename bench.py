@@ -42,9 +42,9 @@ sys.path.insert(0, ROOT)
 H_KV, H_Q, D, CTX = 8, 32, 128, 32768
 K_PAGE_BYTES, V_PAGE_BYTES = 5760, 4608     # packed record + fp16 metadata per (page, kv-head)
 # dram__bytes_read.sum + dram__bytes_write.sum of decode_paged_i8_kernel per page pair, from one ncu capture of the
-# batch-8 case of this workload (182.71 MB for the launch less the 6.66 MB of its 64 edges = 176.05 MB over 16256
+# batch-8 case of this workload (180.75 MB for the launch less the 6.66 MB of its 64 edges = 174.09 MB over 16256
 # pairs).  A figure from a past capture: it has to be re-taken whenever the streaming kernel's data path changes.
-DRAM_BYTES_PER_PAGE_PAIR = 10829
+DRAM_BYTES_PER_PAGE_PAIR = 10709
 
 
 def parse():
