@@ -229,7 +229,12 @@ __device__ __forceinline__ void edge_item(const DecodeArgs &a, const DecodePlan 
       const int w1 = min(ne, w0 + RB);
       if (ok) ok = mbar_wait(bar, *phase & 1u);
       ok = __syncthreads_and(ok) != 0;             // block-uniform: a wait that ran out ends the reduction for everyone
-      if (!ok) break;
+      if (!ok) {
+        // Give the wave still in flight one more bounded chance to land: the row buffer is then not overwritten
+        // under it, and the barrier's phase count stays in step for the block's next edge item.
+        if (__syncthreads_and(mbar_wait(bar, *phase & 1u)) != 0) *phase += 1;
+        break;
+      }
       *phase += 1;
       constexpr int UNR = 8;
       for (int e0 = w0 + warp; e0 < w1; e0 += UNR * EDGE_WARPS) {

@@ -38,6 +38,7 @@ def test_struct_sizes_match_the_header():
     from kitty_b200 import _lib
 
     assert ctypes.sizeof(_lib.KittyCounts) == 32
+    assert ctypes.sizeof(_lib.KittyStepState) == 168          # 3 x kitty_counts + 18 ints (the header says so)
     assert ctypes.sizeof(_lib.KittyLayer) == 8 * 4 + 11 * 8
 
 
