@@ -214,6 +214,7 @@ def test_cache_replay_against_oracle_and_reference(kb, name):
     (2, 16, 2, 32 + 7 * 128 + 31, torch.bfloat16),   # group of 8: two full operand groups of the integer kernel
     (1, 5, 2, 32 + 10 * 128 + 99, torch.float16),    # group of 5: second operand group holds one head
     (3, 18, 1, 32 + 5 * 128 + 64, torch.bfloat16),   # group of 6
+    (8, 32, 9, 32 + 3 * 128 + 5, torch.float16),     # 72 (batch, kv-head) row groups
     (1, 4, 2, 20, torch.float16),                # shorter than the sink
     (1, 4, 2, 33, torch.float16),
     (1, 4, 1, 160, torch.float16),               # exactly sink + one page: no packed value page yet
