@@ -194,36 +194,35 @@ def cpu_reference(ctx: int, steps: int, warmup: int, budget_s: float = 25.0):
 
 
 # --------------------------------------------------------------------------- #
-def build_cache(kb, batch, ctx, extra, device, seed, dtype=torch.bfloat16):
-    cfg = argparse.Namespace(num_hidden_layers=1, head_dim=D, num_key_value_heads=H_KV, num_attention_heads=H_Q,
+def build_cache(kb, batch, ctx, extra, device, seed, dtype=torch.bfloat16, layers=1):
+    cfg = argparse.Namespace(num_hidden_layers=layers, head_dim=D, num_key_value_heads=H_KV, num_attention_heads=H_Q,
                              hidden_size=H_Q * D)
     cache = kb.KittyCache(cfg, batch, ctx + extra + 256, device=device)
     g = torch.Generator(device=device).manual_seed(seed)
-    # the prompt is generated and quantized in slices of 16 sequences to bound transient memory
-    lay = cache.kv_cache[0]
     from kitty_b200 import _lib
 
     p = partition(ctx)
-    for b0 in range(0, batch, 16):
-        b1 = min(batch, b0 + 16)
-        k = torch.randn(b1 - b0, H_KV, ctx, D, generator=g, device=device, dtype=torch.float32)
-        for h in range(H_KV):
-            k[:, h, :, torch.randperm(D, generator=g, device=device)[:4]] *= 8.0
-        k = k.to(dtype)
-        v = torch.randn(b1 - b0, H_KV, ctx, D, generator=g, device=device, dtype=torch.float32).to(dtype)
-        sub = _lib.KittyLayer.from_buffer_copy(lay.c_layer())
-        for name, rows in (("Sink_Buffer_K", 32), ("Sink_Buffer_V", 32), ("Q_Buffer_K", 128), ("Q_Buffer_V", 128),
-                           ("Local_Buffer_V", 128)):
-            setattr(sub, name, getattr(lay, name)[b0].data_ptr())
-        rc = _lib.lib().kitty_prefill_tails(sub, k.data_ptr(), v.data_ptr(), _lib.dtype_code(dtype), k.stride(0), k.stride(1),
-                                            k.stride(2), v.stride(0), v.stride(1), v.stride(2), b1 - b0, ctx, p["sink"],
-                                            p["qbuf_k"], p["local_v"], p["qbuf_v"], _lib.stream_ptr(k.device))
-        _lib.check(rc, "kitty_prefill_tails")
-        kb.quantize_pack_k(k, p["sink"], p["pages_k"], lay.PageTable_K[b0:b1], 0, lay.KeyCache, lay.KeyCache_metadata, 128, 32)
-        kb.quantize_pack_v(v, p["sink"], p["pages_v"], lay.PageTable_V[b0:b1], 0, lay.ValueCache, lay.ValueCache_metadata, 128)
-        del k, v
-    lay.Sink_Count, lay.Q_Buffer_Count_K, lay.Local_Count_V, lay.Q_Buffer_Count_V = p["sink"], p["qbuf_k"], p["local_v"], p["qbuf_v"]
-    lay.PageCount_K, lay.PageCount_V = p["pages_k"], p["pages_v"]
+    for lay in cache.kv_cache:
+        # the prompt is generated and quantized in slices of 16 sequences to bound transient memory
+        for b0 in range(0, batch, 16):
+            b1 = min(batch, b0 + 16)
+            k = torch.randn(b1 - b0, H_KV, ctx, D, generator=g, device=device, dtype=torch.float32)
+            for h in range(H_KV):
+                k[:, h, :, torch.randperm(D, generator=g, device=device)[:4]] *= 8.0
+            k = k.to(dtype)
+            v = torch.randn(b1 - b0, H_KV, ctx, D, generator=g, device=device, dtype=torch.float32).to(dtype)
+            sub = _lib.KittyLayer.from_buffer_copy(lay.c_layer())
+            for name in ("Sink_Buffer_K", "Sink_Buffer_V", "Q_Buffer_K", "Q_Buffer_V", "Local_Buffer_V"):
+                setattr(sub, name, getattr(lay, name)[b0].data_ptr())
+            rc = _lib.lib().kitty_prefill_tails(sub, k.data_ptr(), v.data_ptr(), _lib.dtype_code(dtype), k.stride(0), k.stride(1),
+                                                k.stride(2), v.stride(0), v.stride(1), v.stride(2), b1 - b0, ctx, p["sink"],
+                                                p["qbuf_k"], p["local_v"], p["qbuf_v"], _lib.stream_ptr(k.device))
+            _lib.check(rc, "kitty_prefill_tails")
+            kb.quantize_pack_k(k, p["sink"], p["pages_k"], lay.PageTable_K[b0:b1], 0, lay.KeyCache, lay.KeyCache_metadata, 128, 32)
+            kb.quantize_pack_v(v, p["sink"], p["pages_v"], lay.PageTable_V[b0:b1], 0, lay.ValueCache, lay.ValueCache_metadata, 128)
+            del k, v
+        lay.Sink_Count, lay.Q_Buffer_Count_K, lay.Local_Count_V, lay.Q_Buffer_Count_V = p["sink"], p["qbuf_k"], p["local_v"], p["qbuf_v"]
+        lay.PageCount_K, lay.PageCount_V = p["pages_k"], p["pages_v"]
     torch.cuda.synchronize(device)
     return cache
 
@@ -507,7 +506,7 @@ def seqsplit_measure(kb, device, rank, world, dist, steps, warmup, seq_batch, ex
     NL layers' caches take turns so that every step reads cold pages (NL x 43 MB per sequence > L2) and the steps
     are queued back to back, as the layers of a model are; the same seeds on every rank: same sequences."""
     global H_KV, H_Q
-    from kitty_b200.seqsplit import PartialExchange, seq_split_decode, seq_split_step
+    from kitty_b200.seqsplit import PartialExchange, rank_flags, seq_split_decode, split_pages
 
     saved = (H_KV, H_Q)
     H_KV, H_Q = 4, 28
@@ -516,7 +515,12 @@ def seqsplit_measure(kb, device, rank, world, dist, steps, warmup, seq_batch, ex
         W, K, SB = max(3, warmup), steps, seq_batch
         REP = 5                                        # the median of REP repeats of K steps is reported
         NL = 8 if SB * 8 * 43 <= 4000 else 4
-        caches = [build_cache(kb, SB, ctx, (W + REP * K) // NL + 2, device, seed=4321 + j) for j in range(NL)]
+        if exchange == "step":
+            # one cache of NL layers, as a model has: the token is planned once and every layer is one library call
+            model_cache = build_cache(kb, SB, ctx, (W + REP * K) // NL + 2, device, seed=4321, layers=NL)
+            caches = [model_cache]
+        else:
+            caches = [build_cache(kb, SB, ctx, (W + REP * K) // NL + 2, device, seed=4321 + j) for j in range(NL)]
         lay = caches[0].kv_cache[0]
         g = torch.Generator(device=device).manual_seed(17)
         qs = torch.randn(W + REP * K, SB, H_Q, 1, D, generator=g, device=device).to(torch.bfloat16)
@@ -525,11 +529,19 @@ def seqsplit_measure(kb, device, rank, world, dist, steps, warmup, seq_batch, ex
         xch = PartialExchange(SB * H_Q, device) if (exchange in ("peer", "step") and world > 1) else None
 
         def step(i):
+            if exchange == "step":
+                # one library call per layer step, counters and plan in a device block written once per token
+                cache, li = caches[0], i % NL
+                if li == 0:
+                    lo, hi = split_pages(cache.kv_cache[0].PageCount_V, world, tail_weight)[rank]
+                    cache.plan_step(SB, H_Q, page_begin=lo, page_end=hi, flags=rank_flags(rank, world),
+                                    exchange=xch if world > 1 else None)
+                out = cache.step_layer(li, ks[i], vs[i], qs[i], D ** -0.5)
+                if li == NL - 1:
+                    cache.finish_step()
+                return out
             cache = caches[i % NL]
             layer = cache.kv_cache[0]
-            if exchange == "step":      # one library call per layer step, counters and plan in a device block
-                return seq_split_step(cache, ks[i], vs[i], qs[i], D ** -0.5, rank=rank, world=world, exchange=xch,
-                                      tail_weight=tail_weight)
             cache.update(ks[i], vs[i], 0)
             out = seq_split_decode(qs[i], layer, H_KV, D ** -0.5, rank=rank, world=world,
                                    n_common_pages=layer.PageCount_V, exchange=xch, tail_weight=tail_weight)
@@ -589,8 +601,9 @@ def seqsplit_record(kb, device, rank, world, dist, steps: int = 48, warmup: int 
         r["one_gpu_frac_of_peak"] = packed / (us1 * 1e-6) / 1e9 / peak
         rec[f"batch{sb}"] = r
     rec["collective"] = {"step": "none: as 'peer', with the whole layer step (append, attention, exchange, flush) in one "
-                                 "library call from device-resident counters (kitty_decode_step_exchange); the "
-                                 "one-GPU figure uses the same one-call step (kitty_decode_step)",
+                                 "library call from device-resident counters (kitty_decode_step_exchange) on one "
+                                 "8-layer cache whose token is planned once for all layers, as in a model; the one-GPU "
+                                 "figure uses the same one-call step (kitty_decode_step)",
                          "peer": "none: the attention call's merge step stores the partials into every rank's buffer over "
                                  "NVLink and waits (bounded) for the others (kitty_decode_attn_exchange)",
                          "nccl": "all_gather of [28,130] fp32 per rank + kitty_lse_merge"}

@@ -241,3 +241,43 @@ def test_split_pages_is_a_contiguous_partition_for_any_tail_weight():
     assert [hi - lo for lo, hi in split_pages(1022, 8)] == [128] * 6 + [127] * 2
     sizes = [hi - lo for lo, hi in split_pages(1022, 8, 32)]
     assert sizes[-1] == sizes[0] - 33 and max(sizes[:-1]) - min(sizes[:-1]) <= 1
+
+
+def test_plan_step_split_covers_the_sequence_exactly_once():
+    """kitty_plan_step_split for the ranks of a sequence split: the page ranges of the ranks tile the common pages, the
+    sink belongs to rank 0 only and the tail to the last rank only, every rank plans the same append and flushes, and
+    the exchange sequence number is carried in the state."""
+    import ctypes
+
+    from kitty_b200 import _lib
+    from kitty_b200.seqsplit import rank_flags, split_pages
+    from oracle import kitty_oracle as ko
+
+    p = ko.prefill_partition(32 + 128 * 37 + 100)
+    counts = _lib.KittyCounts()
+    for k, v in {"PageCount_K": p["pages_k"], "PageCount_V": p["pages_v"], "Sink_Count": p["sink"],
+                 "Q_Buffer_Count_K": p["qbuf_k"], "Q_Buffer_Count_V": p["qbuf_v"], "Local_Count_V": p["local_v"],
+                 "Write_Offset_Local_V": 0}.items():
+        setattr(counts, k, v)
+    L = _lib.KittyLayer()
+    L.max_bs, L.max_page, L.h_kv, L.head_dim, L.d_boost, L.page_size, L.sink_size = 2, 64, 4, 128, 32, 128, 32
+    world = 5
+    covered, states = [], []
+    for rank, (lo, hi) in enumerate(split_pages(p["pages_v"], world)):
+        st = _lib.KittyStepState()
+        rc = _lib.lib().kitty_plan_step_split(ctypes.byref(L), ctypes.byref(counts), 1, 28, lo, hi, rank_flags(rank, world),
+                                              17, ctypes.byref(st), None, None)
+        assert rc == 0
+        assert (st.pb, st.pe) == (lo, hi) and st.xchg_seq == 17
+        assert st.has_sink == int(rank == 0) and st.has_tail == int(rank == world - 1)
+        assert st.n_items == 4 * st.nchunk and st.nchunk * st.ch >= hi - lo
+        covered += list(range(st.pb, st.pe))
+        states.append(st)
+    assert covered == list(range(p["pages_v"]))
+    for st in states[1:]:
+        assert [getattr(st.next, f) for f, _ in _lib.KittyCounts._fields_] == \
+               [getattr(states[0].next, f) for f, _ in _lib.KittyCounts._fields_]
+        assert (st.flush_k, st.flush_v) == (states[0].flush_k, states[0].flush_v)
+    st = _lib.KittyStepState()
+    assert _lib.lib().kitty_plan_step_split(ctypes.byref(L), ctypes.byref(counts), 1, 28, 0, -1, 3, -1, ctypes.byref(st),
+                                            None, None) == _lib.KITTY_E_BADARG
