@@ -69,7 +69,11 @@ class KittyCache(Cache):
             return True
         if key_states.shape[-2] != 1 or lengths is not None:
             # a further piece of the prompt (chunked prefill), possibly of a different length per row
-            self._append_chunk(lay, key_states, value_states, lengths)
+            n = key_states.shape[-2]
+            if lay.row_counts is None and (lengths is None or all(int(x) == n for x in lengths)):
+                self._append_chunk_uniform(lay, key_states, value_states)
+            else:
+                self._append_chunk(lay, key_states, value_states, lengths)
             return False
         if lay.row_counts is not None:
             self._append_rows(lay, key_states, value_states, None)
@@ -184,6 +188,66 @@ class KittyCache(Cache):
         for t in range(int(lens.max())):
             self._append_rows(lay, key_states[:, :, t:t + 1], value_states[:, :, t:t + 1], lens > t)
             self._flush_rows(lay)
+
+    def _append_chunk_uniform(self, lay, key_states, value_states) -> None:
+        """A further piece of the prompt, the same n tokens for every row of a layer whose rows share one set of
+        counters: the whole piece in a few launches.  The state afterwards is bit for bit the one n decode steps
+        (append, then flush when a Q-buffer is full) leave behind: the tokens are cast to fp16 as the append kernel
+        casts them; what fits goes to the sink; keys join the key Q-buffer, and every full 128 tokens of
+        [Q-buffer, piece] become a page; values enter the ring of the last 128 tokens at the slot the append kernel
+        would have used (oldest token at Write_Offset_Local_V), the tokens they push out join the value Q-buffer, and
+        every full 128 of those become a page.  The layer keeps its single set of counters."""
+        P, S = lay.PAGE_SIZE, lay.S
+        B = key_states.shape[0]
+        kh = key_states.to(torch.float16)
+        vh = value_states.to(torch.float16)
+        n = kh.shape[2]
+        take = min(n, S - lay.Sink_Count)
+        if take > 0:
+            lay.Sink_Buffer_K[:B, :, lay.Sink_Count:lay.Sink_Count + take] = kh[:, :, :take]
+            lay.Sink_Buffer_V[:B, :, lay.Sink_Count:lay.Sink_Count + take] = vh[:, :, :take]
+            lay.Sink_Count += take
+            kh, vh, n = kh[:, :, take:], vh[:, :, take:], n - take
+        if n == 0:
+            return
+        lay.ensure_pages(lay.PageCount_K + n // P + 2, lay.PageCount_V + n // P + 2)
+        # keys
+        qk = lay.Q_Buffer_Count_K
+        stream = torch.cat([lay.Q_Buffer_K[:B, :, :qk], kh], dim=2) if qk else kh
+        pages, rem = divmod(stream.shape[2], P)
+        if pages:
+            quantize_pack_k(stream, 0, pages, lay.PageTable_K, lay.PageCount_K, lay.KeyCache, lay.KeyCache_metadata,
+                            P, lay.D_BOOSTED, selection=self.selection, div_mode=self.div_mode)
+            lay.PageCount_K += pages
+        if rem:
+            lay.Q_Buffer_K[:B, :, :rem] = stream[:, :, pages * P:]
+        lay.Q_Buffer_Count_K = rem
+        # values: first the ring fills up, then every further token pushes the oldest one out
+        fill = min(n, P - lay.Local_Count_V)
+        if fill > 0:
+            lay.Local_Buffer_V[:B, :, lay.Local_Count_V:lay.Local_Count_V + fill] = vh[:, :, :fill]
+            lay.Local_Count_V += fill
+        m = n - fill
+        if m > 0:
+            w = lay.Write_Offset_Local_V
+            ring = lay.Local_Buffer_V[:B]
+            ordered = torch.roll(ring, shifts=-w, dims=2) if w else ring            # oldest first
+            seq = torch.cat([ordered, vh[:, :, fill:]], dim=2)                       # P + m tokens, oldest first
+            w = (w + m) % P
+            keep = seq[:, :, m:]
+            lay.Local_Buffer_V[:B] = torch.roll(keep, shifts=w, dims=2) if w else keep
+            lay.Write_Offset_Local_V = w
+            qv = lay.Q_Buffer_Count_V
+            stream = torch.cat([lay.Q_Buffer_V[:B, :, :qv], seq[:, :, :m]], dim=2) if qv else seq[:, :, :m]
+            pages, rem = divmod(stream.shape[2], P)
+            if pages:
+                quantize_pack_v(stream, 0, pages, lay.PageTable_V, lay.PageCount_V, lay.ValueCache,
+                                lay.ValueCache_metadata, P, div_mode=self.div_mode)
+                lay.PageCount_V += pages
+            if rem:
+                lay.Q_Buffer_V[:B, :, :rem] = stream[:, :, pages * P:]
+            lay.Q_Buffer_Count_V = rem
+        lay.ensure_pages(lay.PageCount_K + 1, lay.PageCount_V + 1)
 
     def _quantize_prefill_ragged(self, lay, k, v) -> None:
         """Prompt with one length per row: each row is partitioned and quantized as a batch of one (the kernels see a

@@ -159,6 +159,37 @@ def test_prompt_in_pieces_equals_token_by_token_and_one_piece(kb):
         assert ko.rel_err(out[b:b + 1].float().cpu().numpy(), want) <= ATTN_TOL
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_uniform_pieces_take_the_bulk_path_and_equal_token_by_token(kb, dtype):
+    """Pieces of the same length for every row of a layer with one set of counters: a few launches per piece, the
+    layer keeps its single counters, and every buffer and page equals the oracle's after token-by-token appends (the
+    oracle, like the append kernel, stores appended tokens as fp16 — which is what distinguishes this from a longer
+    prefill when the model runs in bf16)."""
+    h_kv, h_q, B = 2, 8, 2
+    first, pieces = 20, [5, 300, 129, 700]
+    total = first + sum(pieces)
+    k, v = make_kv(B, h_kv, total, 128, 23, dtype)
+    cache = kb.KittyCache(_cfg(h_kv, h_q), B, total + 64, device=DEV)
+    assert cache.update(k[:, :, :first].to(DEV), v[:, :, :first].to(DEV), 0) is True
+    cache.quantize_prefill(0)
+    off = first
+    for n in pieces:
+        assert cache.update(k[:, :, off:off + n].to(DEV), v[:, :, off:off + n].to(DEV), 0) is False
+        off += n
+    lay = cache.kv_cache[0]
+    assert lay.row_counts is None and cache.get_seq_length(0) == total
+    lay.make_ragged()                       # only to reuse the row-wise comparison below
+    for b in range(B):
+        oc = ko.OracleKittyCache(1, h_kv, 128, 1, total + 64)
+        oc.update(k[b:b + 1, :, :first], v[b:b + 1, :, :first], 0)
+        oc.quantize_prefill(0)
+        for t in range(first, total):
+            oc.update(k[b:b + 1, :, t:t + 1], v[b:b + 1, :, t:t + 1], 0)
+            oc.quantize_decode(0)
+        _assert_row_equals_oracle(lay, b, oc.kv_cache[0])
+    assert kb.workspace_status(lay) == 0
+
+
 def test_ragged_entry_points_reject_bad_rows(kb):
     import ctypes
 

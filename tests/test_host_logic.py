@@ -281,3 +281,90 @@ def test_plan_step_split_covers_the_sequence_exactly_once():
     st = _lib.KittyStepState()
     assert _lib.lib().kitty_plan_step_split(ctypes.byref(L), ctypes.byref(counts), 1, 28, 0, -1, 3, -1, ctypes.byref(st),
                                             None, None) == _lib.KITTY_E_BADARG
+
+
+class _TokenSim:
+    """Token-by-token model of one layer's queues (kvcache/kitty.py:102-123 and 201-234): tokens are numbers."""
+
+    def __init__(self, S=32, P=128):
+        self.S, self.P = S, P
+        self.sink, self.qk, self.qv, self.pages_k, self.pages_v = [], [], [], [], []
+        self.ring, self.w = [], 0
+
+    def push(self, t):
+        if len(self.sink) < self.S:
+            self.sink.append(t)
+            return
+        self.qk.append(t)
+        if len(self.ring) < self.P:
+            self.ring.append(t)
+        else:
+            self.qv.append(self.ring[self.w])
+            self.ring[self.w] = t
+            self.w = (self.w + 1) % self.P
+        if len(self.qk) == self.P:
+            self.pages_k.append(self.qk)
+            self.qk = []
+        if len(self.qv) == self.P:
+            self.pages_v.append(self.qv)
+            self.qv = []
+
+
+@pytest.mark.parametrize("history,pieces", [
+    (20, [5, 300, 2]),            # the piece straddles the sink; the ring fills and wraps
+    (40, [88, 129, 640]),         # ring not yet full, then exactly full, then several pages at once
+    (32 + 128 + 77, [200, 51]),   # ring already wrapped (write offset != 0)
+])
+def test_a_uniform_piece_of_the_prompt_goes_through_in_bulk(fake, history, pieces):
+    """update() with n > 1 tokens for every row of a layer with one set of counters takes the bulk path: sink, key
+    Q-buffer, value ring (slots and write offset) and value Q-buffer end up exactly as after n single-token appends,
+    the pages receive exactly the tokens the flushes would have packed, and the layer keeps its single counters."""
+    cache_mod, calls = fake
+    cfg = types.SimpleNamespace(num_hidden_layers=1, head_dim=128, num_key_value_heads=1, num_attention_heads=4,
+                                hidden_size=512)
+    cache = cache_mod.KittyCache(cfg, 1, 4096)
+    lay = cache.kv_cache[0]
+    f16 = dict(dtype=torch.float16)
+    lay.Sink_Buffer_K, lay.Sink_Buffer_V = torch.zeros(1, 1, 32, 128, **f16), torch.zeros(1, 1, 32, 128, **f16)
+    lay.Q_Buffer_K, lay.Q_Buffer_V = torch.zeros(1, 1, 128, 128, **f16), torch.zeros(1, 1, 128, 128, **f16)
+    lay.Local_Buffer_V = torch.zeros(1, 1, 128, 128, **f16)
+    sim = _TokenSim()
+    for t in range(1, history + 1):
+        sim.push(t)
+
+    def load_state():
+        lay.Sink_Count, lay.Q_Buffer_Count_K, lay.Q_Buffer_Count_V = len(sim.sink), len(sim.qk), len(sim.qv)
+        lay.Local_Count_V, lay.Write_Offset_Local_V = len(sim.ring), sim.w
+        lay.PageCount_K, lay.PageCount_V = len(sim.pages_k), len(sim.pages_v)
+        for buf, vals in ((lay.Sink_Buffer_K, sim.sink), (lay.Sink_Buffer_V, sim.sink), (lay.Q_Buffer_K, sim.qk),
+                          (lay.Q_Buffer_V, sim.qv), (lay.Local_Buffer_V, sim.ring)):
+            buf.zero_()
+            if vals:
+                buf[0, 0, :len(vals)] = torch.tensor(vals, **f16)[:, None]
+    load_state()
+    packed = {"pack_k": [list(p) for p in sim.pages_k], "pack_v": [list(p) for p in sim.pages_v]}
+    nxt = history + 1
+    for n in pieces:
+        calls.clear()
+        toks = torch.arange(nxt, nxt + n, dtype=torch.float32)
+        chunk = toks[None, None, :, None].expand(1, 1, n, 128).to(torch.float32 if n % 2 else torch.float16)
+        assert cache.update(chunk, chunk, 0) is False
+        for t in range(nxt, nxt + n):
+            sim.push(t)
+        nxt += n
+        for name, a in calls:
+            if name in packed:
+                stream, t_off, pages, _, page_off = a[:5]
+                assert t_off == 0 and page_off == len(packed[name])
+                for p in range(pages):
+                    packed[name].append([int(x) for x in stream[0, 0, 128 * p:128 * (p + 1), 0].float().tolist()])
+        assert lay.row_counts is None
+        assert not any(nm in ("kitty_append", "kitty_append_rows", "kitty_flush_rows") for nm, _ in calls)
+        assert (lay.Sink_Count, lay.Q_Buffer_Count_K, lay.Q_Buffer_Count_V, lay.Local_Count_V, lay.Write_Offset_Local_V,
+                lay.PageCount_K, lay.PageCount_V) == (len(sim.sink), len(sim.qk), len(sim.qv), len(sim.ring), sim.w,
+                                                      len(sim.pages_k), len(sim.pages_v))
+        for buf, vals in ((lay.Sink_Buffer_K, sim.sink), (lay.Sink_Buffer_V, sim.sink), (lay.Q_Buffer_K, sim.qk),
+                          (lay.Q_Buffer_V, sim.qv), (lay.Local_Buffer_V, sim.ring)):
+            assert [int(x) for x in buf[0, 0, :len(vals), 0].tolist()] == vals
+        assert packed["pack_k"] == sim.pages_k and packed["pack_v"] == sim.pages_v
+    assert cache.get_seq_length(0) == nxt - 1
