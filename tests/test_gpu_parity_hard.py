@@ -35,7 +35,7 @@ def _cfg(layers, h_kv, h_q):
 
 
 def _record(name, payload):
-    """Measured rates go to gpurun_out/ (scratch) so that they can be quoted; the assertions are the test."""
+    """Measured rates are also written to a scratch folder so that they can be quoted; the assertions are the test."""
     out = os.path.join(ROOT, "gpurun_out")
     try:
         os.makedirs(out, exist_ok=True)
