@@ -199,9 +199,16 @@ class KittyCache(Cache):
         every full 128 of those become a page.  The layer keeps its single set of counters."""
         P, S = lay.PAGE_SIZE, lay.S
         B = key_states.shape[0]
+        n = key_states.shape[2]
+        # capacity first, before anything is written: the pages this piece completes must exist
+        rest = n - min(n, S - lay.Sink_Count)
+        new_k = (lay.Q_Buffer_Count_K + rest) // P
+        pushed = max(0, rest - (P - lay.Local_Count_V))
+        new_v = (lay.Q_Buffer_Count_V + pushed) // P
+        if lay.PageCount_K + new_k > lay.MAX_PAGE or lay.PageCount_V + new_v > lay.MAX_PAGE:
+            raise _lib.KittyError(_lib.KITTY_E_BADARG, "KittyCache.update: the piece does not fit the cache's pages")
         kh = key_states.to(torch.float16)
         vh = value_states.to(torch.float16)
-        n = kh.shape[2]
         take = min(n, S - lay.Sink_Count)
         if take > 0:
             lay.Sink_Buffer_K[:B, :, lay.Sink_Count:lay.Sink_Count + take] = kh[:, :, :take]

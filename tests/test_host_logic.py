@@ -368,3 +368,22 @@ def test_a_uniform_piece_of_the_prompt_goes_through_in_bulk(fake, history, piece
             assert [int(x) for x in buf[0, 0, :len(vals), 0].tolist()] == vals
         assert packed["pack_k"] == sim.pages_k and packed["pack_v"] == sim.pages_v
     assert cache.get_seq_length(0) == nxt - 1
+
+
+def test_a_piece_that_does_not_fit_is_refused_before_anything_is_written(fake, monkeypatch):
+    cache_mod, calls = fake
+    from kitty_b200 import _lib
+    monkeypatch.setattr(_lib, "strerror", lambda status: "bad argument")
+    cfg = types.SimpleNamespace(num_hidden_layers=1, head_dim=128, num_key_value_heads=1, num_attention_heads=4,
+                                hidden_size=512)
+    cache = cache_mod.KittyCache(cfg, 1, 512)            # 4 pages
+    lay = cache.kv_cache[0]
+    k = torch.zeros(1, 1, 40, 128, dtype=torch.float16)
+    assert cache.update(k, k, 0) is True
+    cache.quantize_prefill(0)
+    before = [getattr(lay, c) for c in COUNTERS]
+    calls.clear()
+    piece = torch.zeros(1, 1, 700, 128, dtype=torch.float16)
+    with pytest.raises(_lib.KittyError):
+        cache.update(piece, piece, 0)
+    assert [getattr(lay, c) for c in COUNTERS] == before and not calls
