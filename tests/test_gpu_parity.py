@@ -101,6 +101,52 @@ def test_quant_fused_selection_bit_exact_with_oracle(kb, dtype, kind, seed):
     assert not kc_h[0].any() and not kc_h[1].any() and not kc_h[7].any()
 
 
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_quant_degenerate_pages_bit_exact_with_oracle(kb, dtype):
+    """Pages that stress the boundary computation and the selection: all zeros; one constant per channel (range 0, the
+    scale floor); every channel with max = -min (the middle boundary sits at zero, where the 16-bit grid is finer
+    than fp32 next to min); values far below the scale floor; values near the top of the type's range; all channels
+    equal (every score ties: lower channel first); a page of two values only."""
+    g = torch.Generator().manual_seed(41)
+    H, P = 2, 7
+    x = torch.zeros(1, H, P * 128, 128)
+    pg = lambda i: x[:, :, 128 * i:128 * (i + 1)]
+    pg(1)[:] = (torch.arange(128) * 0.25 - 9.0)[None, None, None, :]
+    a = torch.randn(1, H, 64, 128, generator=g) * torch.exp(torch.rand(1, H, 1, 128, generator=g) * 3.0)
+    a[:, :, 0] = a.abs().amax(2) * 1.5                      # the largest magnitude of the channel, with both signs below
+    pg(2)[:] = torch.cat([a, -a], dim=2)
+    pg(3)[:] = torch.randn(1, H, 128, 128, generator=g) * 1e-7
+    pg(4)[:] = torch.randn(1, H, 128, 128, generator=g) * (6000.0 if dtype == "f16" else 1e30)
+    pg(5)[:] = torch.randn(1, H, 128, 1, generator=g).expand(1, H, 128, 128)
+    pg(6)[:] = torch.where(torch.rand(1, H, 128, 128, generator=g) < 0.5, torch.tensor(-1.0), torch.tensor(3.0))
+    xd = x.to(TORCH_DT[dtype])
+    kc, km, vc, vm, pt = _buffers(1, H, 8)
+    idx_out = torch.full((1, H, P, 128), 255, dtype=torch.uint8, device=DEV)
+    from kitty_b200 import _lib
+
+    xs = xd.to(DEV)
+    rc = _lib.lib().kitty_quant_pack_k(xs.data_ptr(), _lib.dtype_code(xs.dtype), xs.stride(0), xs.stride(1), xs.stride(2),
+                                       1, H, 0, P, pt.data_ptr(), pt.stride(0), 0, kc.data_ptr(), kc.stride(0),
+                                       km.data_ptr(), idx_out.data_ptr(), _lib.SELECT_FUSED, _lib.DIV_IEEE,
+                                       torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    kb.quantize_pack_v(xs, 0, P, pt, 0, vc, vm, 128)
+    pages = ko.as_f32(xd).reshape(1, H, P, 128, 128)
+    idx = ko.rank_channels(ko.channel_score(pages, dtype, "exact"), 32, "stable")
+    assert np.array_equal(idx_out.cpu().numpy(), idx)
+    rec, meta = ko.quantize_k_pages(pages.reshape(-1, 128, 128), idx.reshape(-1, 128), 32)
+    rec, meta = rec.reshape(H, P, 5248), meta.reshape(H, P, 128, 2)
+    vrec, vmeta = ko.quantize_v_pages(pages.reshape(-1, 128, 128))
+    vrec, vmeta = vrec.reshape(H, P, 4096), vmeta.reshape(H, P, 128, 2)
+    kc_h, km_h = kc.cpu().numpy().reshape(-1, H, 5248), _f16_bits(km)
+    vc_h, vm_h = vc.cpu().numpy().reshape(-1, H, 4096), _f16_bits(vm)
+    for p in range(P):
+        assert np.array_equal(kc_h[p], rec[:, p]), p
+        assert np.array_equal(km_h[p], meta[:, p].view(np.int16)), p
+        assert np.array_equal(vc_h[p], vrec[:, p]), p
+        assert np.array_equal(vm_h[p], vmeta[:, p].view(np.int16)), p
+
+
 def test_quant_torch_selection_is_tie_equivalent(kb):
     """selection='torch' (the reference's host prologue run on the device) and the
     fused rule agree on the score found at every rank."""
