@@ -70,7 +70,7 @@ def parse():
     ap.add_argument("--seq-batch", type=int, default=1, help="seqsplit workload: sequences (the named config has 1)")
     ap.add_argument("--tail-weight", type=int, default=0,
                     help="seqsplit workload: packed pages the last rank's tail is counted as when the pages are split")
-    ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer", "step"],
+    ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer", "step", "graph"],
                     help="seqsplit workload: combine the partials with an NCCL all-gather + merge kernel, or inside "
                          "the merge kernel over peer memory")
     return ap.parse_args()
@@ -515,9 +515,9 @@ def seqsplit_measure(kb, device, rank, world, dist, steps, warmup, seq_batch, ex
         W, K, SB = max(3, warmup), steps, seq_batch
         REP = 5                                        # the median of REP repeats of K steps is reported
         NL = 8 if SB * 8 * 43 <= 4000 else 4
-        if exchange == "step":
+        if exchange in ("step", "graph"):
             # one cache of NL layers, as a model has: the token is planned once and every layer is one library call
-            model_cache = build_cache(kb, SB, ctx, (W + REP * K) // NL + 2, device, seed=4321, layers=NL)
+            model_cache = build_cache(kb, SB, ctx, (W + REP * K) // NL + 4, device, seed=4321, layers=NL)
             caches = [model_cache]
         else:
             caches = [build_cache(kb, SB, ctx, (W + REP * K) // NL + 2, device, seed=4321 + j) for j in range(NL)]
@@ -526,7 +526,34 @@ def seqsplit_measure(kb, device, rank, world, dist, steps, warmup, seq_batch, ex
         qs = torch.randn(W + REP * K, SB, H_Q, 1, D, generator=g, device=device).to(torch.bfloat16)
         ks = torch.randn(W + REP * K, SB, H_KV, 1, D, generator=g, device=device).to(torch.bfloat16)
         vs = torch.randn(W + REP * K, SB, H_KV, 1, D, generator=g, device=device).to(torch.bfloat16)
-        xch = PartialExchange(SB * H_Q, device) if (exchange in ("peer", "step") and world > 1) else None
+        xch = PartialExchange(SB * H_Q, device) if (exchange in ("peer", "step", "graph") and world > 1) else None
+        graph = [None, 0]                              # the captured token, eager tokens done
+
+        def token_graphed():
+            """One token = NL layer steps of the NL-layer cache, replayed from a CUDA graph as a model's decode step
+            is (hf_adapter.GraphedDecoder): plan on the host, one graph launch, counters advanced on the host.  The
+            captured layer calls read static inputs; counters, plan and exchange sequence come from the device block
+            that plan_step() rewrites, so the same graph serves every token."""
+            cache = caches[0]
+            lo, hi = split_pages(cache.kv_cache[0].PageCount_V, world, tail_weight)[rank]
+            cache.plan_step(SB, H_Q, page_begin=lo, page_end=hi, flags=rank_flags(rank, world),
+                            exchange=xch if world > 1 else None)
+
+            def layers():
+                for li in range(NL):
+                    cache.step_layer(li, ks[li], vs[li], qs[li], D ** -0.5)
+            if graph[0] is None and graph[1] < 2:
+                graph[1] += 1
+                layers()                               # eager first: lazy initialisation must not be captured
+            elif graph[0] is None:
+                g_ = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g_):
+                    layers()
+                graph[0] = g_
+                g_.replay()                            # capture records without running
+            else:
+                graph[0].replay()
+            cache.finish_step()
 
         def step(i):
             if exchange == "step":
@@ -548,8 +575,12 @@ def seqsplit_measure(kb, device, rank, world, dist, steps, warmup, seq_batch, ex
             cache.quantize_decode(0)
             return out
 
-        for i in range(W):
-            step(i)
+        if exchange == "graph":
+            for _ in range(W // NL + 3):
+                token_graphed()
+        else:
+            for i in range(W):
+                step(i)
         reps = []
         for r in range(REP):
             torch.cuda.synchronize(device)
@@ -558,11 +589,15 @@ def seqsplit_measure(kb, device, rank, world, dist, steps, warmup, seq_batch, ex
             torch.cuda.synchronize(device)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            for i in range(K):
-                step(W + r * K + i)
+            if exchange == "graph":
+                for _ in range(K // NL):
+                    token_graphed()
+            else:
+                for i in range(K):
+                    step(W + r * K + i)
             e1.record()
             e1.synchronize()
-            reps.append(e0.elapsed_time(e1))
+            reps.append(e0.elapsed_time(e1) * (K / ((K // NL) * NL) if exchange == "graph" else 1.0))
         t = torch.tensor(reps, device=device, dtype=torch.float64)
         if dist is not None and world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)          # per repeat: the slowest rank
@@ -583,24 +618,30 @@ def seqsplit_record(kb, device, rank, world, dist, steps: int = 48, warmup: int 
            "unit": "us"}
     peak, _ = hbm_peak()
     for sb in (1, 8):
-        one = torch.zeros(1, device=device, dtype=torch.float64)
+        one = torch.zeros(2, device=device, dtype=torch.float64)
         if rank == 0:
             us1, packed, _ = seqsplit_measure(kb, device, 0, 1, None, steps, warmup, sb, "step", 0)
             one[0] = us1
+            one[1], _, _ = seqsplit_measure(kb, device, 0, 1, None, steps, warmup, sb, "graph", 0)
         if world > 1:
             dist.all_reduce(one, op=dist.ReduceOp.MAX)
         us1 = float(one[0])
-        r = {"one_gpu_us": us1}
-        for ex in ("step", "peer", "nccl"):
+        r = {"one_gpu_us": us1, "one_gpu_graph_us": float(one[1])}
+        for ex in ("graph", "step", "peer", "nccl"):
             us, packed, _ = seqsplit_measure(kb, device, rank, world, dist, steps, warmup, sb, ex, 0)
+            base = float(one[1]) if ex == "graph" else us1      # like with like: graph replay against graph replay
             r[f"{ex}_us"] = us
-            r[f"{ex}_speedup_vs_one_gpu"] = us1 / us
-            r[f"{ex}_strong_scaling_efficiency"] = us1 / us / world
+            r[f"{ex}_speedup_vs_one_gpu"] = base / us
+            r[f"{ex}_strong_scaling_efficiency"] = base / us / world
             r[f"{ex}_packed_kv_GBps_aggregate"] = packed / (us * 1e-6) / 1e9
         r["packed_kv_bytes"] = packed
         r["one_gpu_frac_of_peak"] = packed / (us1 * 1e-6) / 1e9 / peak
         rec[f"batch{sb}"] = r
-    rec["collective"] = {"step": "none: as 'peer', with the whole layer step (append, attention, exchange, flush) in one "
+    rec["collective"] = {"graph": "none: as 'step', with the layer steps of one token replayed from a CUDA graph (plan on "
+                                  "the host, one graph launch per token, as hf_adapter.GraphedDecoder runs a model), so "
+                                  "that no rank waits for another rank's host; the one-GPU figure next to it "
+                                  "(one_gpu_graph_us) is replayed from a graph too",
+                         "step": "none: as 'peer', with the whole layer step (append, attention, exchange, flush) in one "
                                  "library call from device-resident counters (kitty_decode_step_exchange) on one "
                                  "8-layer cache whose token is planned once for all layers, as in a model; the one-GPU "
                                  "figure uses the same one-call step (kitty_decode_step)",
@@ -633,7 +674,7 @@ def seqsplit_workload(args):
                                                  f"{NL} layers' caches in turn (cold pages every step), steps queued back to back",
                                      "collective": "peer-memory exchange inside the attention call" if args.exchange != "nccl"
                                      and world > 1 else "all_gather of [28,130] fp32 per rank + merge",
-                                     "calls_per_step": 1 if args.exchange == "step" else 3}}))
+                                     "calls_per_step": 1 if args.exchange in ("step", "graph") else 3}}))
     if dist is not None:
         dist.destroy_process_group()
 
