@@ -289,3 +289,64 @@ def test_workspace_bound_serves_every_smaller_batch(kb):
                            torch.randn(37, 16, 1, 128, generator=g).half().to(DEV), 0.088)
     cache.finish_step()
     assert out.shape == (37, 1, 16, 128) and torch.isfinite(out.float()).all()
+
+
+# --------------------------------------------------------------------------- #
+# randomised shapes, layouts and value distributions of the bulk quantize
+# --------------------------------------------------------------------------- #
+@pytest.mark.parametrize("trial", range(20))
+def test_quant_randomised_shapes_and_distributions_bit_exact(kb, trial):
+    """Keys (in-kernel selection) and values of random small shapes, contiguous or strided, from five families of
+    data — per-channel scales, integer-valued (ties and lattice effects), per-token scales, sparse outliers,
+    all-positive with a per-channel offset — against the oracle, bit for bit."""
+    from kitty_b200 import _lib
+
+    rng = np.random.default_rng(123 + trial)
+    dtype = ["f16", "bf16"][trial % 2]
+    tdt = {"f16": torch.float16, "bf16": torch.bfloat16}[dtype]
+    B, H, P = int(rng.integers(1, 3)), int(rng.integers(1, 5)), int(rng.integers(1, 6))
+    off = int(rng.integers(0, 3)) * 8
+    T = off + P * 128 + int(rng.integers(0, 40))
+    g = torch.Generator().manual_seed(1000 + trial)
+    x = torch.randn(B, H, T, 128, generator=g)
+    kind = trial % 5
+    if kind == 0:
+        x = x * torch.exp(torch.rand(1, H, 1, 128, generator=g) * 4.0)
+    elif kind == 1:
+        x = torch.round(x * 3)
+    elif kind == 2:
+        x = x * torch.exp(torch.randn(B, H, T, 1, generator=g) * 2.0)
+    elif kind == 3:
+        x = torch.where(torch.rand(B, H, T, 128, generator=g) < 0.02, x * 50, x * 0.01)
+    else:
+        x = x.abs() + torch.rand(1, H, 1, 128, generator=g) * 10
+    xd = x.to(tdt)
+    xs = xd.transpose(1, 2).contiguous().to(DEV).transpose(1, 2) if trial % 3 == 0 else xd.to(DEV)
+    npg = B * P + 3
+    kc = torch.zeros(npg, H * 5248, dtype=torch.uint8, device=DEV)
+    km = torch.zeros(npg, H, 128, 2, dtype=torch.float16, device=DEV)
+    vc = torch.zeros(npg, H * 4096, dtype=torch.uint8, device=DEV)
+    vm = torch.zeros(npg, H, 128, 2, dtype=torch.float16, device=DEV)
+    pt = torch.arange(B * P, dtype=torch.int64, device=DEV).view(B, P) + 1
+    idx_out = torch.full((B, H, P, 128), 255, dtype=torch.uint8, device=DEV)
+    rc = _lib.lib().kitty_quant_pack_k(xs.data_ptr(), _lib.dtype_code(xs.dtype), xs.stride(0), xs.stride(1), xs.stride(2),
+                                       B, H, off, P, pt.data_ptr(), pt.stride(0), 0, kc.data_ptr(), kc.stride(0),
+                                       km.data_ptr(), idx_out.data_ptr(), _lib.SELECT_FUSED, _lib.DIV_IEEE,
+                                       torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    kb.quantize_pack_v(xs, off, P, pt, 0, vc, vm, 128)
+    pages = ko.as_f32(xd)[:, :, off:off + P * 128].reshape(B, H, P, 128, 128)
+    idx = ko.rank_channels(ko.channel_score(pages, dtype, "exact"), 32, "stable")
+    assert np.array_equal(idx_out.cpu().numpy(), idx)
+    rec, meta = ko.quantize_k_pages(pages.reshape(-1, 128, 128), idx.reshape(-1, 128), 32)
+    rec, meta = rec.reshape(B, H, P, 5248), meta.reshape(B, H, P, 128, 2)
+    vrec, vmeta = ko.quantize_v_pages(pages.reshape(-1, 128, 128))
+    vrec, vmeta = vrec.reshape(B, H, P, 4096), vmeta.reshape(B, H, P, 128, 2)
+    kch, kmh = kc.cpu().numpy().reshape(-1, H, 5248), km.cpu().numpy().view(np.int16)
+    vch, vmh = vc.cpu().numpy().reshape(-1, H, 4096), vm.cpu().numpy().view(np.int16)
+    for b in range(B):
+        for p in range(P):
+            pid = b * P + p + 1
+            assert np.array_equal(kch[pid], rec[b, :, p]) and np.array_equal(kmh[pid], meta[b, :, p].view(np.int16))
+            assert np.array_equal(vch[pid], vrec[b, :, p]) and np.array_equal(vmh[pid], vmeta[b, :, p].view(np.int16))
+    assert not kch[0].any() and not vch[0].any()          # page row 0 is not in the table: untouched
