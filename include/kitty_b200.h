@@ -100,6 +100,21 @@ int kitty_quant_pack_v(const void *value, int dtype, int64_t stride_b, int64_t s
                        int64_t page_table_stride_b, int32_t page_offset, uint8_t *cache,
                        int64_t cache_stride_page, void *cache_meta, int div_mode, void *stream);
 
+/* quantize_pack_k and quantize_pack_v of one prompt in ONE launch: the pair of calls the reference's prefill always
+ * issues back to back (kvcache/kitty.py:126-192: keys at :143, values at :175).  Arguments as in the two
+ * functions above, the key ones prefixed k_, the value ones v_; both halves are validated before anything is
+ * launched.  With 16-bit input and KITTY_DIV_IEEE the key tiles are dispatched first and the value tiles fill the
+ * SMs that the last wave of key tiles leaves free; otherwise this is the two launches.  Results are bit-identical to
+ * the two separate calls. */
+int kitty_quant_pack_kv(const void *key, const void *value, int dtype, int64_t k_stride_b, int64_t k_stride_h,
+                        int64_t k_stride_t, int64_t v_stride_b, int64_t v_stride_h, int64_t v_stride_t, int32_t B,
+                        int32_t H, int64_t k_t_offset, int32_t k_pages, const int64_t *k_page_table,
+                        int64_t k_page_table_stride_b, int32_t k_page_offset, uint8_t *k_cache,
+                        int64_t k_cache_stride_page, void *k_cache_meta, uint8_t *idx_io, int select,
+                        int64_t v_t_offset, int32_t v_pages, const int64_t *v_page_table,
+                        int64_t v_page_table_stride_b, int32_t v_page_offset, uint8_t *v_cache,
+                        int64_t v_cache_stride_page, void *v_cache_meta, int div_mode, void *stream);
+
 /* The full-precision copies of KittyCache.quantize_prefill (kvcache/kitty.py:137-141,
  * 164-172) in one launch: the first `sink` tokens into the sink buffers, the last
  * qbuf_k keys into Q_Buffer_K, the last local_v values into Local_Buffer_V and the

@@ -19,7 +19,8 @@ SELECT_FUSED, SELECT_SUPPLIED = 0, 1
 DIV_IEEE, DIV_FULL = 0, 1
 
 EXPORTS = [
-    "kitty_version", "kitty_strerror", "kitty_quant_pack_k", "kitty_quant_pack_v", "kitty_prefill_tails",
+    "kitty_version", "kitty_strerror", "kitty_quant_pack_k", "kitty_quant_pack_v", "kitty_quant_pack_kv",
+    "kitty_prefill_tails",
     "kitty_append", "kitty_flush", "kitty_decode_workspace_bytes", "kitty_workspace_status", "kitty_decode_attn",
     "kitty_lse_merge", "kitty_decode_attn_static", "kitty_plan_step", "kitty_decode_step",
     "kitty_lse_exchange_bytes", "kitty_lse_exchange_merge", "kitty_decode_attn_exchange", "kitty_rope_qk",
@@ -81,6 +82,10 @@ def lib() -> C.CDLL:
     L.kitty_quant_pack_v.restype = C.c_int
     L.kitty_quant_pack_v.argtypes = [vp, C.c_int, i64, i64, i64, i32, i32, i64, i32, vp, i64, i32, vp, i64, vp,
                                      C.c_int, vp]
+    L.kitty_quant_pack_kv.restype = C.c_int
+    L.kitty_quant_pack_kv.argtypes = [vp, vp, C.c_int, i64, i64, i64, i64, i64, i64, i32, i32,
+                                      i64, i32, vp, i64, i32, vp, i64, vp, vp, C.c_int,
+                                      i64, i32, vp, i64, i32, vp, i64, vp, C.c_int, vp]
     L.kitty_prefill_tails.restype = C.c_int
     L.kitty_prefill_tails.argtypes = [C.POINTER(KittyLayer), vp, vp, C.c_int, i64, i64, i64, i64, i64, i64, i32, i64,
                                       i32, i32, i32, i32, vp]

@@ -19,7 +19,7 @@ from transformers.cache_utils import Cache
 
 from . import _lib
 from .layer_state import KVCache_Layer
-from .quant_pack import quantize_pack_k, quantize_pack_v
+from .quant_pack import quantize_pack_k, quantize_pack_kv, quantize_pack_v
 
 
 class KittyCache(Cache):
@@ -326,14 +326,12 @@ class KittyCache(Cache):
         lay.Q_Buffer_Count_K = qbuf_k
         lay.Local_Count_V = local_v
         lay.Q_Buffer_Count_V = qbuf_v
-        if pages_k > 0:
-            quantize_pack_k(k, sink, pages_k, lay.PageTable_K, 0, lay.KeyCache, lay.KeyCache_metadata, P,
-                            lay.D_BOOSTED, selection=self.selection, div_mode=self.div_mode)
-            lay.PageCount_K += pages_k
-        if pages_v > 0:
-            quantize_pack_v(v, sink, pages_v, lay.PageTable_V, 0, lay.ValueCache, lay.ValueCache_metadata, P,
-                            div_mode=self.div_mode)
-            lay.PageCount_V += pages_v
+        # keys and values in one library call (one launch where the options allow it)
+        quantize_pack_kv(k, sink, pages_k, lay.PageTable_K, 0, lay.KeyCache, lay.KeyCache_metadata,
+                         v, sink, pages_v, lay.PageTable_V, 0, lay.ValueCache, lay.ValueCache_metadata, P,
+                         lay.D_BOOSTED, selection=self.selection, div_mode=self.div_mode)
+        lay.PageCount_K += pages_k
+        lay.PageCount_V += pages_v
         lay.key_states = None
         lay.value_states = None
 

@@ -80,3 +80,45 @@ def quantize_pack_v(value_states: torch.Tensor, value_states_t_offset: int, valu
                                        page_offset_v, cache.data_ptr(), cache.stride(0), cache_metadata.data_ptr(),
                                        div_mode, _lib.stream_ptr(x.device))
     _lib.check(rc, "kitty_quant_pack_v")
+
+
+def quantize_pack_kv(key_states: torch.Tensor, key_states_t_offset: int, key_states_page_count: int,
+                     page_table_k: torch.Tensor, page_offset_k: int, key_cache: torch.Tensor,
+                     key_cache_metadata: torch.Tensor, value_states: torch.Tensor, value_states_t_offset: int,
+                     value_states_page_count: int, page_table_v: torch.Tensor, page_offset_v: int,
+                     value_cache: torch.Tensor, value_cache_metadata: torch.Tensor, page_size: int, d_boost: int, *,
+                     selection: str = "fused", div_mode: int = _lib.DIV_IEEE) -> None:
+    """quantize_pack_k followed by quantize_pack_v as the reference's prefill issues them (kvcache/kitty.py:143, :175),
+    in one library call: with 16-bit input, in-kernel selection and IEEE division both run in ONE launch in which the
+    value tiles fill the SMs that the last wave of key tiles leaves free.  Results are bit-identical to the two
+    separate calls; any other combination of options makes the two calls."""
+    B, H, _, D = key_states.shape
+    one_call = (selection == "fused" and key_states_page_count > 0 and value_states_page_count > 0
+                and key_states.dtype == value_states.dtype and tuple(value_states.shape[:2]) == (B, H))
+    if not one_call:
+        if key_states_page_count > 0:
+            quantize_pack_k(key_states, key_states_t_offset, key_states_page_count, page_table_k, page_offset_k,
+                            key_cache, key_cache_metadata, page_size, d_boost, selection=selection, div_mode=div_mode)
+        if value_states_page_count > 0:
+            quantize_pack_v(value_states, value_states_t_offset, value_states_page_count, page_table_v, page_offset_v,
+                            value_cache, value_cache_metadata, page_size, div_mode=div_mode)
+        return
+    if page_size != 128 or D != 128 or d_boost != 32 or value_states.shape[3] != 128:
+        raise ValueError("kitty_b200 kernels are built for page_size=128, D=128, d_boost=32")
+    assert key_states_t_offset + page_size * key_states_page_count <= key_states.shape[2]
+    assert value_states_t_offset + page_size * value_states_page_count <= value_states.shape[2]
+    k, dt, ksb, ksh, kst = _src_args(key_states)
+    v, _, vsb, vsh, vst = _src_args(value_states)
+    for pt in (page_table_k, page_table_v):
+        assert pt.dtype == torch.int64 and pt.stride(1) == 1
+    for c, m in ((key_cache, key_cache_metadata), (value_cache, value_cache_metadata)):
+        assert c.dtype == torch.uint8 and c.stride(1) == 1 and m.is_contiguous()
+    rc = _lib.lib().kitty_quant_pack_kv(k.data_ptr(), v.data_ptr(), dt, ksb, ksh, kst, vsb, vsh, vst, B, H,
+                                        key_states_t_offset, key_states_page_count, page_table_k.data_ptr(),
+                                        page_table_k.stride(0), page_offset_k, key_cache.data_ptr(),
+                                        key_cache.stride(0), key_cache_metadata.data_ptr(), None, _lib.SELECT_FUSED,
+                                        value_states_t_offset, value_states_page_count, page_table_v.data_ptr(),
+                                        page_table_v.stride(0), page_offset_v, value_cache.data_ptr(),
+                                        value_cache.stride(0), value_cache_metadata.data_ptr(), div_mode,
+                                        _lib.stream_ptr(k.device))
+    _lib.check(rc, "kitty_quant_pack_kv")

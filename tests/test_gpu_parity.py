@@ -147,6 +147,29 @@ def test_quant_degenerate_pages_bit_exact_with_oracle(kb, dtype):
         assert np.array_equal(vm_h[p], vmeta[:, p].view(np.int16)), p
 
 
+@pytest.mark.parametrize("dtype,strided,pk,pv", [("bf16", False, 5, 5), ("f16", True, 4, 3), ("bf16", True, 2, 6),
+                                                 ("f32", False, 3, 3)])
+def test_quant_keys_and_values_in_one_call_equal_the_two_calls(kb, dtype, strided, pk, pv):
+    """kitty_quant_pack_kv (one launch for 16-bit input) against kitty_quant_pack_k + kitty_quant_pack_v: every byte
+    of the four destination buffers, with different page counts, offsets and page-table offsets for keys and values."""
+    B, H = 2, 3
+    T = 40 + max(pk, pv) * 128 + 9
+    k, v = make_kv(B, H, T, 128, 31, TORCH_DT[dtype], "loguniform")
+    if strided:
+        ks = k.transpose(1, 2).contiguous().to(DEV).transpose(1, 2)
+        vs = v.transpose(1, 2).contiguous().to(DEV).transpose(1, 2)
+    else:
+        ks, vs = k.to(DEV), v.to(DEV)
+    one = _buffers(B, H, 8)
+    two = _buffers(B, H, 8)
+    kb.quantize_pack_kv(ks, 32, pk, one[4], 1, one[0], one[1], vs, 40, pv, one[4], 2, one[2], one[3], 128, 32)
+    kb.quantize_pack_k(ks, 32, pk, two[4], 1, two[0], two[1], 128, 32)
+    kb.quantize_pack_v(vs, 40, pv, two[4], 2, two[2], two[3], 128)
+    for a, b in zip(one[:4], two[:4]):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+    assert one[0].any() and one[2].any()
+
+
 def test_quant_torch_selection_is_tie_equivalent(kb):
     """selection='torch' (the reference's host prologue run on the device) and the
     fused rule agree on the score found at every rank."""

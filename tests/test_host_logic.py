@@ -69,6 +69,15 @@ def fake(monkeypatch):
     monkeypatch.setattr(_lib, "stream_ptr", lambda d: 0)
     monkeypatch.setattr(cache_mod, "quantize_pack_k", lambda *a, **k: calls.append(("pack_k", a)))
     monkeypatch.setattr(cache_mod, "quantize_pack_v", lambda *a, **k: calls.append(("pack_v", a)))
+
+    def pack_kv(k, k_off, pk, ptk, pok, kc, km, v, v_off, pv, ptv, pov, vc, vm, P, d_boost, **kw):
+        # the prefill's one call for both: recorded as the two calls it stands for
+        if pk > 0:
+            calls.append(("pack_k", (k, k_off, pk, ptk, pok, kc, km, P, d_boost)))
+        if pv > 0:
+            calls.append(("pack_v", (v, v_off, pv, ptv, pov, vc, vm, P)))
+
+    monkeypatch.setattr(cache_mod, "quantize_pack_kv", pack_kv)
     return cache_mod, calls
 
 
