@@ -218,23 +218,17 @@ class KittyCache(Cache):
         if n == 0:
             return
         lay.ensure_pages(lay.PageCount_K + n // P + 2, lay.PageCount_V + n // P + 2)
-        # keys
+        # keys: [key Q-buffer, piece]
         qk = lay.Q_Buffer_Count_K
-        stream = torch.cat([lay.Q_Buffer_K[:B, :, :qk], kh], dim=2) if qk else kh
-        pages, rem = divmod(stream.shape[2], P)
-        if pages:
-            quantize_pack_k(stream, 0, pages, lay.PageTable_K, lay.PageCount_K, lay.KeyCache, lay.KeyCache_metadata,
-                            P, lay.D_BOOSTED, selection=self.selection, div_mode=self.div_mode)
-            lay.PageCount_K += pages
-        if rem:
-            lay.Q_Buffer_K[:B, :, :rem] = stream[:, :, pages * P:]
-        lay.Q_Buffer_Count_K = rem
+        stream_k = torch.cat([lay.Q_Buffer_K[:B, :, :qk], kh], dim=2) if qk else kh
+        pages_k, rem_k = divmod(stream_k.shape[2], P)
         # values: first the ring fills up, then every further token pushes the oldest one out
         fill = min(n, P - lay.Local_Count_V)
         if fill > 0:
             lay.Local_Buffer_V[:B, :, lay.Local_Count_V:lay.Local_Count_V + fill] = vh[:, :, :fill]
             lay.Local_Count_V += fill
         m = n - fill
+        stream_v, pages_v, rem_v = None, 0, lay.Q_Buffer_Count_V
         if m > 0:
             w = lay.Write_Offset_Local_V
             ring = lay.Local_Buffer_V[:B]
@@ -245,15 +239,23 @@ class KittyCache(Cache):
             lay.Local_Buffer_V[:B] = torch.roll(keep, shifts=w, dims=2) if w else keep
             lay.Write_Offset_Local_V = w
             qv = lay.Q_Buffer_Count_V
-            stream = torch.cat([lay.Q_Buffer_V[:B, :, :qv], seq[:, :, :m]], dim=2) if qv else seq[:, :, :m]
-            pages, rem = divmod(stream.shape[2], P)
-            if pages:
-                quantize_pack_v(stream, 0, pages, lay.PageTable_V, lay.PageCount_V, lay.ValueCache,
-                                lay.ValueCache_metadata, P, div_mode=self.div_mode)
-                lay.PageCount_V += pages
-            if rem:
-                lay.Q_Buffer_V[:B, :, :rem] = stream[:, :, pages * P:]
-            lay.Q_Buffer_Count_V = rem
+            stream_v = torch.cat([lay.Q_Buffer_V[:B, :, :qv], seq[:, :, :m]], dim=2) if qv else seq[:, :, :m]
+            pages_v, rem_v = divmod(stream_v.shape[2], P)
+        # the full pages of both streams in one library call
+        if pages_k or pages_v:
+            quantize_pack_kv(stream_k, 0, pages_k, lay.PageTable_K, lay.PageCount_K, lay.KeyCache,
+                             lay.KeyCache_metadata, stream_v if stream_v is not None else stream_k, 0, pages_v,
+                             lay.PageTable_V, lay.PageCount_V, lay.ValueCache, lay.ValueCache_metadata, P,
+                             lay.D_BOOSTED, selection=self.selection, div_mode=self.div_mode)
+            lay.PageCount_K += pages_k
+            lay.PageCount_V += pages_v
+        if rem_k:
+            lay.Q_Buffer_K[:B, :, :rem_k] = stream_k[:, :, pages_k * P:]
+        lay.Q_Buffer_Count_K = rem_k
+        if stream_v is not None:
+            if rem_v:
+                lay.Q_Buffer_V[:B, :, :rem_v] = stream_v[:, :, pages_v * P:]
+            lay.Q_Buffer_Count_V = rem_v
         lay.ensure_pages(lay.PageCount_K + 1, lay.PageCount_V + 1)
 
     def _quantize_prefill_ragged(self, lay, k, v) -> None:
