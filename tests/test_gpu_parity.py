@@ -168,6 +168,36 @@ def test_quant_keys_and_values_in_one_call_equal_the_two_calls(kb, dtype, stride
     for a, b in zip(one[:4], two[:4]):
         assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))
     assert one[0].any() and one[2].any()
+    # the same through the C entry point with SUPPLIED index bytes (those the in-kernel selection just produced)
+    from kitty_b200 import _lib
+
+    idx = torch.full((B, H, pk, 128), 255, dtype=torch.uint8, device=DEV)
+    kb.quantize_pack_k(ks, 32, pk, two[4], 1, two[0], two[1], 128, 32)
+    rc = _lib.lib().kitty_quant_pack_k(ks.data_ptr(), _lib.dtype_code(ks.dtype), ks.stride(0), ks.stride(1), ks.stride(2),
+                                       B, H, 32, pk, two[4].data_ptr(), two[4].stride(0), 1, two[0].data_ptr(),
+                                       two[0].stride(0), two[1].data_ptr(), idx.data_ptr(), _lib.SELECT_FUSED,
+                                       _lib.DIV_IEEE, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0 and int(idx.max()) <= 32
+    three = _buffers(B, H, 8)
+    rc = _lib.lib().kitty_quant_pack_kv(ks.data_ptr(), vs.data_ptr(), _lib.dtype_code(ks.dtype), ks.stride(0), ks.stride(1),
+                                        ks.stride(2), vs.stride(0), vs.stride(1), vs.stride(2), B, H, 32, pk,
+                                        three[4].data_ptr(), three[4].stride(0), 1, three[0].data_ptr(),
+                                        three[0].stride(0), three[1].data_ptr(), idx.data_ptr(), _lib.SELECT_SUPPLIED,
+                                        40, pv, three[4].data_ptr(), three[4].stride(0), 2, three[2].data_ptr(),
+                                        three[2].stride(0), three[3].data_ptr(), _lib.DIV_IEEE,
+                                        torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    for a, b in zip(three[:4], two[:4]):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+    # a bad argument in the value half is reported before the key half is launched
+    rc = _lib.lib().kitty_quant_pack_kv(ks.data_ptr(), vs.data_ptr(), _lib.dtype_code(ks.dtype), ks.stride(0), ks.stride(1),
+                                        ks.stride(2), vs.stride(0), vs.stride(1), vs.stride(2), B, H, 32, pk,
+                                        three[4].data_ptr(), three[4].stride(0), 1, three[0].data_ptr(),
+                                        three[0].stride(0), three[1].data_ptr(), None, _lib.SELECT_FUSED,
+                                        40, pv, None, three[4].stride(0), 2, three[2].data_ptr(),
+                                        three[2].stride(0), three[3].data_ptr(), _lib.DIV_IEEE,
+                                        torch.cuda.current_stream().cuda_stream)
+    assert rc == _lib.KITTY_E_BADARG
 
 
 def test_quant_torch_selection_is_tie_equivalent(kb):
